@@ -1,0 +1,65 @@
+"""sp_aurora_b200: the sequence-parallel attention hot path of sp-aurora (ring,
+Ulysses and hybrid attention, forward and backward) on NVIDIA B200 (sm_100a).
+
+The export list follows sp_aurora/__init__.py:59-122; the `sp_aurora_*` names
+are the spellings the reference's documentation uses for the ring functions.
+All compute goes through libspaurora_sm100.so (hand-written CUDA, C ABI in
+include/spa.h); importing this package fails if that library is not built.
+"""
+from ._lib import SpaError, check_status, device_info, launch_count  # noqa: F401  (loads the .so)
+from .local_attn import (  # noqa: F401
+    flash_attn_backward,
+    flash_attn_forward,
+    update_out_and_lse,
+)
+from .ring import (  # noqa: F401
+    RingComm,
+    RingFlashAttnFunc,
+    ring_flash_attn_backward,
+    ring_flash_attn_forward,
+    ring_flash_attn_func,
+    ring_flash_attn_kvpacked_func,
+    ring_flash_attn_qkvpacked_func,
+)
+from .all_to_all import (  # noqa: F401
+    SeqAllToAll4D,
+    SeqAllToAll5D,
+    all_to_all_4D,
+    all_to_all_5D,
+    seq_all_to_all_4d_inference,
+)
+from .ulysses import (  # noqa: F401
+    AttnType,
+    UlyssesAttention,
+    UlyssesFlashAttnFunc,
+    ulysses_flash_attn_func,
+    ulysses_flash_attn_kvpacked_func,
+    ulysses_flash_attn_qkvpacked_func,
+)
+from .hybrid import (  # noqa: F401
+    PROCESS_GROUP,
+    LongContextAttention,
+    LongContextAttentionQKVPacked,
+    destroy_seq_parallel_pg,
+    set_seq_parallel_pg,
+)
+
+# Names used by the reference's README and tests for the ring entry points.
+sp_aurora_func = ring_flash_attn_func
+sp_aurora_kvpacked_func = ring_flash_attn_kvpacked_func
+sp_aurora_qkvpacked_func = ring_flash_attn_qkvpacked_func
+
+HAS_LONG_CTX_ATTN = True
+HAS_FLASH_ATTN = True
+
+
+def is_available() -> bool:
+    """True when a CUDA device of compute capability 10.x is present
+    (counterpart of sp_aurora/sycl_bindings/bindings.cpp:362 is_available)."""
+    import torch
+    if not torch.cuda.is_available():
+        return False
+    return torch.cuda.get_device_capability()[0] == 10
+
+
+__version__ = "0.1.0"

@@ -1,0 +1,533 @@
+// Flash-attention backward for sm_100a (tcgen05 + TMEM + TMA).
+//
+// One CTA owns a 128-key K/V tile of one kv head and walks over every 64-row
+// query tile (of every query head in its GQA group) that can see those keys.
+// Scores are computed TRANSPOSED (rows = keys, columns = queries) so that the
+// probabilities P^T and dS^T land in shared memory already K-major for the
+// dV / dK products:
+//     S^T  = K  Q^T          dP^T = V dO^T
+//     P^T  = exp2(S^T*scale*log2e - lse*log2e)      (global lse)
+//     dS^T = P^T * (dP^T - delta)
+//     dV  += P^T dO          dK  += dS^T Q          dQ^T = K^T dS   (-> atomics)
+// dV/dK stay in TMEM for the whole walk; dQ^T (rows = head dim, columns =
+// queries) is drained each iteration with coalesced fp32 reductions into the
+// caller's dq accumulator. The softmax scale is applied once on the way out.
+//
+// Algorithm source: the per-step flash backward that the ring loop of
+// sp_aurora/ring_flash_attn.py:97-152 expects (the reference's own
+// sp_aurora/intel_flash_attn.py:129 is a stub); formulas as in the manual
+// backward of sp_aurora/intel_ulysses_attn.py:403-426.
+//
+// CTA = 6 warps: 0-3 compute group (thread = key row / dQ^T lane), 4 = TMA
+// producer, 5 = MMA issuer and TMEM owner.
+// TMEM columns: S^T [0,64) dP^T [64,128) dV [128,128+D) dK [256,256+D) dQ^T [384,448).
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+
+#include <type_traits>
+
+#include "spa_internal.h"
+#include "tc05.cuh"
+
+namespace spa {
+namespace {
+
+constexpr int kTileKV = 128;
+constexpr int kTileQ = 64;
+constexpr int kThreads = 192;
+constexpr int kStages = 3;
+constexpr float kLog2e = 1.4426950408889634f;
+
+constexpr uint32_t kColS = 0, kColDP = 64, kColDV = 128, kColDK = 256, kColDQ = 384;
+
+struct BwdParams {
+  int B, Sq, Sk, Hq, Hkv;
+  int causal, causal_off;
+  int dkv_fp32, dkv_accumulate;
+  int n_kvblk;
+  float scale, scale_log2;
+  const float* lse;
+  const float* delta;
+  float* dq_acc;
+  void* dk;
+  void* dv;
+  int* status;
+};
+
+template <int D>
+struct BwdSmem {
+  static constexpr int kKVSlab = kTileKV * 128;             // 16 KB
+  static constexpr int kKVTile = (D / 64) * kKVSlab;         // K or V tile
+  static constexpr int kQSlab = kTileQ * 128;                // 8 KB
+  static constexpr int kQTile = (D / 64) * kQSlab;           // Q or dO tile
+  static constexpr int kStageBytes = 2 * kQTile;             // Q + dO
+  static constexpr int kPBytes = kTileKV * 128;              // 128 keys x 64 q (2 B)
+  static constexpr int kKOff = 0;
+  static constexpr int kVOff = kKOff + kKVTile;
+  static constexpr int kStageOff = kVOff + kKVTile;
+  static constexpr int kPOff = kStageOff + kStages * kStageBytes;
+  static constexpr int kDSOff = kPOff + kPBytes;
+  static constexpr int kRowOff = kDSOff + kPBytes;           // lse2/delta [2][2][64] floats
+  static constexpr int kBarOff = kRowOff + 2 * 2 * 64 * 4;
+  static constexpr int kNumBars = 1 + 2 * kStages + 6;
+  static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
+};
+
+template <typename T>
+__device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+template <int D, typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
+                      const __grid_constant__ CUtensorMap tm_k,
+                      const __grid_constant__ CUtensorMap tm_v,
+                      const __grid_constant__ CUtensorMap tm_do, const BwdParams p) {
+  using L = BwdSmem<D>;
+  constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOff);
+  uint64_t* kv_full = bars;
+  uint64_t* qdo_full = bars + 1;
+  uint64_t* qdo_empty = qdo_full + kStages;
+  uint64_t* sdp_full = qdo_empty + kStages;
+  uint64_t* sdp_free = sdp_full + 1;
+  uint64_t* pds_full = sdp_free + 1;
+  uint64_t* mma_done = pds_full + 1;
+  uint64_t* dq_free = mma_done + 1;
+  uint64_t* row_ready = dq_free + 1;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
+  volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float* row_buf = reinterpret_cast<float*>(smem + L::kRowOff);  // [buf][lse2|delta][64]
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  // Work decode: kv heads fastest, then batch, then KV tiles in ascending order
+  // (under a causal mask the first tiles see the most queries: longest first).
+  int w = blockIdx.x;
+  const int g = w % p.Hkv;
+  w /= p.Hkv;
+  const int b = w % p.B;
+  w /= p.B;
+  const int kvblk = w;
+  const int kv0 = kvblk * kTileKV;
+  const int G = p.Hq / p.Hkv;
+
+  // Query tiles that can see this K/V tile.
+  const int i_end = (p.Sq + kTileQ - 1) / kTileQ;
+  int i_start = 0;
+  if (p.causal) {
+    const long long first_q = (long long)kv0 - p.causal_off;  // smallest query index seeing kv0
+    if (first_q > 0) i_start = (int)min((long long)i_end, first_q / kTileQ);
+  }
+  const int n_q = i_end - i_start;
+  const int n_it = n_q * G;
+
+  if (threadIdx.x == 0) {
+    *cta_abort = 0;
+    mbar_init(kv_full, 1);
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&qdo_full[i], 1);
+      mbar_init(&qdo_empty[i], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_free, 128);
+    mbar_init(pds_full, 128);
+    mbar_init(mma_done, 1);
+    mbar_init(dq_free, 128);
+    mbar_init(row_ready, 128);
+    fence_mbar_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == 5) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  WaitCtx wc{p.status, cta_abort};
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ TMA
+    if (lane == 0 && n_it > 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      tma_prefetch_desc(&tm_do);
+      mbar_arrive_expect_tx(kv_full, 2 * L::kKVTile);
+      for (int s = 0; s < D / 64; ++s) {
+        tma_load_4d(smem + L::kKOff + s * L::kKVSlab, &tm_k, kv_full, s * 64, kv0, g, b);
+        tma_load_4d(smem + L::kVOff + s * L::kKVSlab, &tm_v, kv_full, s * 64, kv0, g, b);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        const int slot = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        if (!mbar_wait(&qdo_empty[slot], ph ^ 1, wc, 100, it)) break;
+        const int hq = g * G + it / n_q;
+        const int q0 = (i_start + it % n_q) * kTileQ;
+        uint8_t* st = smem + L::kStageOff + slot * L::kStageBytes;
+        mbar_arrive_expect_tx(&qdo_full[slot], L::kStageBytes);
+        for (int s = 0; s < D / 64; ++s) {
+          tma_load_4d(st + s * L::kQSlab, &tm_q, &qdo_full[slot], s * 64, q0, hq, b);
+          tma_load_4d(st + L::kQTile + s * L::kQSlab, &tm_do, &qdo_full[slot], s * 64, q0, hq, b);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA
+    if (lane == 0 && n_it > 0) {
+      constexpr uint32_t idesc_sdp = make_idesc(128, kTileQ, kBf16, false, false);
+      constexpr uint32_t idesc_dkv = make_idesc(128, D, kBf16, false, true);
+      constexpr uint32_t idesc_dq = make_idesc(128, kTileQ, kBf16, true, true);
+      constexpr uint32_t kLboK = (D == 128) ? L::kKVSlab : 0;  // D=64: lanes 64-127 mirror 0-63
+      const uint32_t k_base = smem_u32(smem + L::kKOff);
+      const uint32_t v_base = smem_u32(smem + L::kVOff);
+      const uint32_t st_base = smem_u32(smem + L::kStageOff);
+      const uint32_t p_base = smem_u32(smem + L::kPOff);
+      const uint32_t ds_base = smem_u32(smem + L::kDSOff);
+      bool ok = mbar_wait(kv_full, 0, wc, 200, 0);
+      tc_fence_after();
+
+      auto issue_sdp = [&](int it) -> bool {
+        const int slot = it % kStages;
+        if (!mbar_wait(&qdo_full[slot], (it / kStages) & 1, wc, 201, it)) return false;
+        tc_fence_after();
+        const uint32_t qb = st_base + slot * L::kStageBytes;
+        const uint32_t dob = qb + L::kQTile;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t aoff = (kk / 4) * L::kKVSlab + (kk % 4) * 32;
+          const uint32_t boff = (kk / 4) * L::kQSlab + (kk % 4) * 32;
+          mma_ss(tmem_base + kColS, smem_desc_sw128(k_base + aoff, 16, 1024),
+                 smem_desc_sw128(qb + boff, 16, 1024), idesc_sdp, kk > 0);
+        }
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t aoff = (kk / 4) * L::kKVSlab + (kk % 4) * 32;
+          const uint32_t boff = (kk / 4) * L::kQSlab + (kk % 4) * 32;
+          mma_ss(tmem_base + kColDP, smem_desc_sw128(v_base + aoff, 16, 1024),
+                 smem_desc_sw128(dob + boff, 16, 1024), idesc_sdp, kk > 0);
+        }
+        mma_commit(sdp_full);
+        return true;
+      };
+
+      if (ok) ok = issue_sdp(0);
+      for (int it = 0; it < n_it && ok; ++it) {
+        if (it + 1 < n_it) {
+          ok = mbar_wait(sdp_free, it & 1, wc, 202, it);
+          if (!ok) break;
+          tc_fence_after();
+          ok = issue_sdp(it + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(pds_full, it & 1, wc, 203, it);
+        if (!ok) break;
+        tc_fence_after();
+        const int slot = it % kStages;
+        const uint32_t qb = st_base + slot * L::kStageBytes;
+        const uint32_t dob = qb + L::kQTile;
+        // dV += P^T dO ; dK += dS^T Q   (A K-major over queries, B MN-major)
+#pragma unroll
+        for (int kk = 0; kk < kTileQ / 16; ++kk)
+          mma_ss(tmem_base + kColDV, smem_desc_sw128(p_base + kk * 32, 16, 1024),
+                 smem_desc_sw128(dob + kk * 2048, L::kQSlab, 1024), idesc_dkv, (it > 0 || kk > 0));
+#pragma unroll
+        for (int kk = 0; kk < kTileQ / 16; ++kk)
+          mma_ss(tmem_base + kColDK, smem_desc_sw128(ds_base + kk * 32, 16, 1024),
+                 smem_desc_sw128(qb + kk * 2048, L::kQSlab, 1024), idesc_dkv, (it > 0 || kk > 0));
+        // dQ^T = K^T dS : A = K tile read MN-major (M = head dim), B = dS^T tile
+        // read MN-major (N = queries), contraction over the 128 keys.
+        if (it > 0) {
+          ok = mbar_wait(dq_free, (it - 1) & 1, wc, 204, it);
+          if (!ok) break;
+          tc_fence_after();
+        }
+#pragma unroll
+        for (int kk = 0; kk < kTileKV / 16; ++kk)
+          mma_ss(tmem_base + kColDQ, smem_desc_sw128(k_base + kk * 2048, kLboK, 1024),
+                 smem_desc_sw128(ds_base + kk * 2048, 16, 1024), idesc_dq, kk > 0);
+        mma_commit(mma_done);
+        mma_commit(&qdo_empty[slot]);
+      }
+    }
+  } else {
+    // -------------------------------------------------------------- compute
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;          // key row in tile, and dQ^T lane (head-dim index)
+    const int kidx = kv0 + r;
+    const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
+    const uint32_t t_s = tmem_base + lane_field + kColS;
+    const uint32_t t_dp = tmem_base + lane_field + kColDP;
+    const uint32_t t_dv = tmem_base + lane_field + kColDV;
+    const uint32_t t_dk = tmem_base + lane_field + kColDK;
+    const uint32_t t_dq = tmem_base + lane_field + kColDQ;
+    uint8_t* p_row = smem + L::kPOff;
+    uint8_t* ds_row = smem + L::kDSOff;
+    const bool key_ok = kidx < p.Sk;
+    bool ok = true;
+
+    // Row statistics of a query tile: threads 0-63 fetch lse (pre-multiplied by
+    // log2 e), threads 64-127 fetch delta. +inf lse makes out-of-range rows give P = 0.
+    auto fetch_rowstat = [&](int it) -> float {
+      const int hq = g * G + it / n_q;
+      const int q0 = (i_start + it % n_q) * kTileQ;
+      const int c = r & 63;
+      const int qi = q0 + c;
+      const size_t idx = ((size_t)b * p.Hq + hq) * p.Sq + qi;
+      if (r < 64) return qi < p.Sq ? p.lse[idx] * kLog2e : INFINITY;
+      return qi < p.Sq ? p.delta[idx] : 0.f;
+    };
+    // dQ^T drain of iteration `it`: thread = head-dim index, columns = queries.
+    auto drain_dq = [&](int it) {
+      const int hq = g * G + it / n_q;
+      const int q0 = (i_start + it % n_q) * kTileQ;
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        uint32_t v[32];
+        tmem_ld32(t_dq + c * 32, v);
+        tmem_ld_wait();
+        if (r < D) {
+          float* base = p.dq_acc + (((size_t)b * p.Sq + q0 + c * 32) * p.Hq + hq) * D + r;
+          const int nvalid = min(32, p.Sq - (q0 + c * 32));
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < nvalid) atomicAdd(base + (size_t)i * p.Hq * D, __uint_as_float(v[i]) * p.scale);
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(dq_free);
+    };
+
+    if (n_it > 0) {
+      row_buf[(0 * 2 + (r >> 6)) * 64 + (r & 63)] = fetch_rowstat(0);
+      mbar_arrive(row_ready);
+    }
+
+    for (int it = 0; it < n_it; ++it) {
+      float next_stat = 0.f;
+      if (it + 1 < n_it) next_stat = fetch_rowstat(it + 1);
+
+      ok = warp_wait(sdp_full, it & 1, wc, 300, it);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sr[64], dpr[64];
+      tmem_ld32(t_s, sr);
+      tmem_ld32(t_s + 32, sr + 32);
+      tmem_ld32(t_dp, dpr);
+      tmem_ld32(t_dp + 32, dpr + 32);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(sdp_free);
+
+      // Row statistics of this iteration are in shared memory once all 128
+      // threads of the group have arrived (bounded, unlike a bar.sync).
+      ok = warp_wait(row_ready, it & 1, wc, 305, it);
+      if (!ok) break;
+      const float* lse2 = row_buf + ((it & 1) * 2 + 0) * 64;
+      const float* dlt = row_buf + ((it & 1) * 2 + 1) * 64;
+      const int q0 = (i_start + it % n_q) * kTileQ;
+      // Visible iff kidx <= q + off  <=>  column c >= kidx - off - q0.
+      int c_min = 0;
+      if (p.causal) {
+        const long long cm = (long long)kidx - p.causal_off - q0;
+        c_min = (int)max(0ll, min(cm, 64ll));
+      }
+      if (!key_ok) c_min = 64;
+
+      uint32_t pp[32], dsp[32];
+#pragma unroll
+      for (int c4 = 0; c4 < 16; ++c4) {
+        const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
+        const float4 d4 = *reinterpret_cast<const float4*>(dlt + 4 * c4);
+        const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+        const float dv[4] = {d4.x, d4.y, d4.z, d4.w};
+        float pv[4], dsv[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = 4 * c4 + u;
+          float pe = fast_exp2(fmaf(__uint_as_float(sr[c]), p.scale_log2, -lv[u]));
+          if (c < c_min) pe = 0.f;
+          pv[u] = pe;
+          dsv[u] = pe * (__uint_as_float(dpr[c]) - dv[u]);
+        }
+        pp[2 * c4] = pack2<T>(pv[0], pv[1]);
+        pp[2 * c4 + 1] = pack2<T>(pv[2], pv[3]);
+        dsp[2 * c4] = pack2<T>(dsv[0], dsv[1]);
+        dsp[2 * c4 + 1] = pack2<T>(dsv[2], dsv[3]);
+      }
+
+      if (it > 0) {
+        // dV/dK/dQ MMAs of the previous iteration have read P^T/dS^T and
+        // produced dQ^T(it-1).
+        ok = warp_wait(mma_done, (it - 1) & 1, wc, 310, it);
+        if (!ok) break;
+        tc_fence_after();
+      }
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        const uint32_t off = sw128_chunk_off(r, c);
+        *reinterpret_cast<uint4*>(p_row + off) =
+            make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
+        *reinterpret_cast<uint4*>(ds_row + off) =
+            make_uint4(dsp[4 * c], dsp[4 * c + 1], dsp[4 * c + 2], dsp[4 * c + 3]);
+      }
+      if (it + 1 < n_it) {
+        row_buf[(((it + 1) & 1) * 2 + (r >> 6)) * 64 + (r & 63)] = next_stat;
+        mbar_arrive(row_ready);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_full);
+
+      if (it > 0) drain_dq(it - 1);
+    }
+
+    if (ok && n_it > 0) {
+      ok = warp_wait(mma_done, (n_it - 1) & 1, wc, 320, n_it);
+      if (ok) {
+        tc_fence_after();
+        drain_dq(n_it - 1);
+      }
+    }
+
+    // ------------------------------------------------------------- epilogue
+    if (ok) {
+      const size_t row_off = (((size_t)b * p.Sk + kidx) * p.Hkv + g) * D;
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const uint32_t taddr = which == 0 ? t_dv : t_dk;
+        const float mul = which == 0 ? 1.f : p.scale;
+        void* dst_base = which == 0 ? p.dv : p.dk;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) {
+          float o[32];
+          if (n_it > 0) {
+            uint32_t v[32];
+            tmem_ld32(taddr + c * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * mul;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0.f;
+          }
+          if (!key_ok) continue;
+          if (p.dkv_fp32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(dst_base) + row_off +
+                                                    c * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float4 x = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+              if (p.dkv_accumulate) {
+                const float4 y = dst[i];
+                x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+              }
+              dst[i] = x;
+            }
+          } else {
+            T* drow = reinterpret_cast<T*>(dst_base) + row_off + c * 32;
+            if (p.dkv_accumulate) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] += static_cast<float>(drow[i]);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(drow);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              dst[i] = make_uint4(pack2<T>(o[8 * i], o[8 * i + 1]), pack2<T>(o[8 * i + 2], o[8 * i + 3]),
+                                  pack2<T>(o[8 * i + 4], o[8 * i + 5]),
+                                  pack2<T>(o[8 * i + 6], o[8 * i + 7]));
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (*cta_abort) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+    __syncthreads();
+  }
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D, typename T>
+int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
+  using L = BwdSmem<D>;
+  CUtensorMap tq, tk, tv, tdo;
+  if (encode_rows_map(&tq, a->q, is_bf16, D, a->Sq, a->Hq, a->B, a->q_ss, a->q_sh, a->q_sb, kTileQ))
+    return SPA_ECUDA;
+  if (encode_rows_map(&tdo, a->dout, is_bf16, D, a->Sq, a->Hq, a->B, a->do_ss, a->do_sh, a->do_sb,
+                      kTileQ))
+    return SPA_ECUDA;
+  if (encode_rows_map(&tk, a->k, is_bf16, D, a->Sk, a->Hkv, a->B, a->k_ss, a->k_sh, a->k_sb, kTileKV))
+    return SPA_ECUDA;
+  if (encode_rows_map(&tv, a->v, is_bf16, D, a->Sk, a->Hkv, a->B, a->v_ss, a->v_sh, a->v_sb, kTileKV))
+    return SPA_ECUDA;
+  BwdParams p;
+  p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.Hq = a->Hq; p.Hkv = a->Hkv;
+  p.causal = a->causal; p.causal_off = a->causal_off;
+  p.dkv_fp32 = a->dkv_fp32; p.dkv_accumulate = a->dkv_accumulate;
+  p.n_kvblk = ceil_div(a->Sk, kTileKV);
+  p.scale = a->scale; p.scale_log2 = a->scale * kLog2e;
+  p.lse = a->lse; p.delta = a->delta; p.dq_acc = a->dq_acc; p.dk = a->dk; p.dv = a->dv;
+  p.status = device_status_word();
+  if (!p.status) return SPA_ECUDA;
+  const int smem_bytes = L::kTotal + 1024;
+  auto kern = attn_bwd_sm100_kernel<D, T>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (e != cudaSuccess) {
+      set_error("cudaFuncSetAttribute(bwd sm100): %s", cudaGetErrorString(e));
+      return SPA_ECUDA;
+    }
+    attr_set = true;
+  }
+  const long long grid = (long long)p.n_kvblk * a->B * a->Hkv;
+  if (grid <= 0 || grid > 0x7fffffffll) {
+    set_error("bwd grid out of range");
+    return SPA_EINVAL;
+  }
+  kern<<<(unsigned)grid, kThreads, smem_bytes, (cudaStream_t)a->stream>>>(tq, tk, tv, tdo, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("bwd sm100 launch: %s", cudaGetErrorString(e));
+    return SPA_ECUDA;
+  }
+  return SPA_OK;
+}
+
+}  // namespace
+
+int launch_bwd_sm100(const spa_bwd_args* a) {
+  const bool bf = a->dtype == SPA_DTYPE_BF16;
+  if (a->D == 128) {
+    return bf ? launch_bwd_typed<128, __nv_bfloat16>(a, 1) : launch_bwd_typed<128, __half>(a, 0);
+  } else if (a->D == 64) {
+    return bf ? launch_bwd_typed<64, __nv_bfloat16>(a, 1) : launch_bwd_typed<64, __half>(a, 0);
+  }
+  set_error("tensor-core backward supports head_dim 64 and 128, got %d", a->D);
+  return SPA_EUNSUPPORTED;
+}
+
+}  // namespace spa

@@ -1,0 +1,487 @@
+// extern "C" surface of libspaurora_sm100 plus the HBM-bound helper kernels
+// (delta row sums, stand-alone out/lse merge, fp32 -> element-type cast,
+// Ulysses pack/unpack row permutation) and host-side plumbing: argument
+// validation, TMA descriptor encoding, the per-device status word.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <math.h>
+#include <stdarg.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include <atomic>
+#include <mutex>
+
+#include "spa_internal.h"
+
+namespace spa {
+
+// ------------------------------------------------------------------ errors
+static thread_local char g_err[512] = "";
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+static std::atomic<long long> g_launches{0};
+static inline void note_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+
+// --------------------------------------------------------- device status word
+static std::mutex g_status_mu;
+static int* g_status[64] = {nullptr};
+
+int* device_status_word() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("cudaGetDevice failed");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(g_status_mu);
+  if (!g_status[dev]) {
+    int* p = nullptr;
+    cudaError_t e = cudaMalloc(&p, 4 * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(p, 0, 4 * sizeof(int));
+    if (e != cudaSuccess) {
+      set_error("status word allocation: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_status[dev] = p;
+  }
+  return g_status[dev];
+}
+
+// ------------------------------------------------------- TMA descriptor encode
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaError_t e =
+        cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres);
+    if (e == cudaSuccess && qres == cudaDriverEntryPointSuccess) fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+int encode_rows_map(CUtensorMap* map, const void* ptr, int is_bf16, int D, int64_t S, int H, int B,
+                    int64_t stride_s, int64_t stride_h, int64_t stride_b, int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled entry point not available");
+    return -1;
+  }
+  // Size-1 dimensions may carry arbitrary strides; give them harmless ones.
+  if (S == 1) stride_s = D;
+  if (H == 1) stride_h = D;
+  if (B == 1) stride_b = D;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)stride_s * 2, (cuuint64_t)stride_h * 2,
+                           (cuuint64_t)stride_b * 2};
+  cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (((uintptr_t)ptr & 15) || (strides[0] & 15) || (strides[1] & 15) || (strides[2] & 15)) {
+    set_error("tensor base and strides must be 16-byte aligned for TMA");
+    return -1;
+  }
+  CUresult r = fn(map, is_bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                  4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled failed with code %d (D=%d S=%lld H=%d B=%d)", (int)r, D,
+              (long long)S, H, B);
+    return -1;
+  }
+  return 0;
+}
+
+// ---------------------------------------------------------------- helpers
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float4 ld4(const T* p);
+template <>
+__device__ __forceinline__ float4 ld4<float>(const float* p) {
+  return *reinterpret_cast<const float4*>(p);
+}
+template <>
+__device__ __forceinline__ float4 ld4<__nv_bfloat16>(const __nv_bfloat16* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <>
+__device__ __forceinline__ float4 ld4<__half>(const __half* p) {
+  const uint2 u = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&u.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&u.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+template <typename T>
+__device__ __forceinline__ void st4(T* p, float4 v);
+template <>
+__device__ __forceinline__ void st4<float>(float* p, float4 v) {
+  *reinterpret_cast<float4*>(p) = v;
+}
+template <>
+__device__ __forceinline__ void st4<__nv_bfloat16>(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a);
+  u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+template <>
+__device__ __forceinline__ void st4<__half>(__half* p, float4 v) {
+  __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+  uint2 u;
+  u.x = *reinterpret_cast<uint32_t*>(&a);
+  u.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = u;
+}
+
+// One thread per 4 elements; D/4 consecutive threads (<= 32, a power of two,
+// inside one warp) share a [b,s,h] row. Rows are numbered (b*S + s)*H + h.
+struct RowIdx {
+  int b, s, h;
+};
+__device__ __forceinline__ RowIdx decode_row(long long row, int S, int H) {
+  RowIdx r;
+  r.h = (int)(row % H);
+  row /= H;
+  r.s = (int)(row % S);
+  r.b = (int)(row / S);
+  return r;
+}
+
+template <typename T>
+__global__ void delta_kernel(const T* __restrict__ out, int64_t o_sb, int64_t o_ss, int64_t o_sh,
+                             const T* __restrict__ dout, int64_t d_sb, int64_t d_ss, int64_t d_sh,
+                             float* __restrict__ delta, int B, int S, int H, int D) {
+  const int tpr = D / 4;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gid / tpr;
+  const int c = (int)(gid % tpr) * 4;
+  const long long nrows = (long long)B * S * H;
+  float acc = 0.f;
+  RowIdx r = {0, 0, 0};
+  if (row < nrows) {
+    r = decode_row(row, S, H);
+    const float4 a = ld4<T>(out + r.b * o_sb + r.s * o_ss + r.h * o_sh + c);
+    const float4 d = ld4<T>(dout + r.b * d_sb + r.s * d_ss + r.h * d_sh + c);
+    acc = a.x * d.x + a.y * d.y + a.z * d.z + a.w * d.w;
+  }
+  for (int o = tpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  if (row < nrows && c == 0) delta[((size_t)r.b * H + r.h) * S + r.s] = acc;
+}
+
+template <typename T>
+__global__ void merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse,
+                             const T* __restrict__ bo, int64_t bo_sb, int64_t bo_ss, int64_t bo_sh,
+                             const float* __restrict__ blse, int B, int S, int H, int D) {
+  const int tpr = D / 4;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gid / tpr;
+  const int c = (int)(gid % tpr) * 4;
+  const long long nrows = (long long)B * S * H;
+  const bool ok = row < nrows;
+  float lse_new = 0.f;
+  size_t li = 0;
+  if (ok) {
+    const RowIdx r = decode_row(row, S, H);
+    li = ((size_t)r.b * H + r.h) * S + r.s;
+    const float lo = lse[li], lb = blse[li];
+    const float mx = fmaxf(lo, lb);
+    float w_old = 0.f, w_blk = 0.f;
+    lse_new = mx;
+    if (mx != -INFINITY) {
+      const float eo = expf(lo - mx), eb = expf(lb - mx);
+      const float sum = eo + eb;
+      lse_new = mx + logf(sum);
+      w_old = eo / sum;
+      w_blk = eb / sum;
+    }
+    float* ap = out_acc + (size_t)row * D + c;
+    const float4 a = *reinterpret_cast<const float4*>(ap);
+    const float4 x = ld4<T>(bo + r.b * bo_sb + r.s * bo_ss + r.h * bo_sh + c);
+    *reinterpret_cast<float4*>(ap) =
+        make_float4(w_old * a.x + w_blk * x.x, w_old * a.y + w_blk * x.y, w_old * a.z + w_blk * x.z,
+                    w_old * a.w + w_blk * x.w);
+  }
+  __syncwarp();  // every thread of the row has read the old lse
+  if (ok && c == 0) lse[li] = lse_new;
+}
+
+template <typename T>
+__global__ void cast_kernel(const float* __restrict__ src, T* __restrict__ dst, int64_t d_sb,
+                            int64_t d_ss, int64_t d_sh, int B, int S, int H, int D, float alpha) {
+  const int tpr = D / 4;
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gid / tpr;
+  const int c = (int)(gid % tpr) * 4;
+  if (row >= (long long)B * S * H) return;
+  const RowIdx r = decode_row(row, S, H);
+  float4 v = *reinterpret_cast<const float4*>(src + (size_t)row * D + c);
+  v.x *= alpha; v.y *= alpha; v.z *= alpha; v.w *= alpha;
+  st4<T>(dst + r.b * d_sb + r.s * d_ss + r.h * d_sh + c, v);
+}
+
+struct PermuteParams {
+  int64_t n[4];
+  int64_t ss[4];
+  int64_t ds[4];
+  int64_t vec_per_row;
+  int64_t total_vec;
+};
+// Thread = one 16-byte vector; consecutive threads walk a row, then the next
+// logical row, so both sides see full-line accesses.
+__global__ void permute_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                                    const PermuteParams p) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total_vec; i += stride) {
+    const int64_t v = i % p.vec_per_row;
+    int64_t r = i / p.vec_per_row;
+    const int64_t i3 = r % p.n[3]; r /= p.n[3];
+    const int64_t i2 = r % p.n[2]; r /= p.n[2];
+    const int64_t i1 = r % p.n[1]; r /= p.n[1];
+    const int64_t i0 = r;
+    const int64_t so = i0 * p.ss[0] + i1 * p.ss[1] + i2 * p.ss[2] + i3 * p.ss[3] + v * 16;
+    const int64_t dof = i0 * p.ds[0] + i1 * p.ds[1] + i2 * p.ds[2] + i3 * p.ds[3] + v * 16;
+    *reinterpret_cast<uint4*>(dst + dof) = *reinterpret_cast<const uint4*>(src + so);
+  }
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    set_error("%s launch: %s", what, cudaGetErrorString(e));
+    return SPA_ECUDA;
+  }
+  return SPA_OK;
+}
+
+bool valid_head_dim(int D) { return D == 32 || D == 64 || D == 128; }
+
+bool force_simt() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("SPA_FORCE_CUDA_CORE");
+    v = (e && e[0] == '1') ? 1 : 0;
+  }
+  return v == 1;
+}
+
+}  // namespace
+}  // namespace spa
+
+using namespace spa;
+
+extern "C" {
+
+const char* spa_last_error(void) { return g_err; }
+
+int64_t spa_launch_count(void) { return g_launches.load(); }
+
+int spa_device_info(int32_t device, int64_t info[6]) {
+  cudaDeviceProp prop;
+  cudaError_t e = cudaGetDeviceProperties(&prop, device);
+  if (e != cudaSuccess) {
+    set_error("cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    return SPA_ECUDA;
+  }
+  info[0] = prop.multiProcessorCount;
+  info[1] = prop.major;
+  info[2] = prop.minor;
+  info[3] = (int64_t)prop.sharedMemPerBlockOptin;
+  info[4] = prop.l2CacheSize;
+  info[5] = (int64_t)(prop.totalGlobalMem >> 20);
+  return SPA_OK;
+}
+
+int spa_check_status(void) {
+  int* st = device_status_word();
+  if (!st) return SPA_ECUDA;
+  int h[4] = {0, 0, 0, 0};
+  cudaError_t e = cudaMemcpy(h, st, sizeof(h), cudaMemcpyDeviceToHost);
+  if (e != cudaSuccess) {
+    set_error("status read: %s", cudaGetErrorString(e));
+    return SPA_ECUDA;
+  }
+  if (h[0] != 0) {
+    set_error("device-side bounded wait gave up: code %d block %d site %d iteration %d", h[0], h[1],
+              h[2], h[3]);
+    cudaMemset(st, 0, sizeof(h));
+    return SPA_ETIMEOUT;
+  }
+  return SPA_OK;
+}
+
+static int validate_common(int B, int Sq, int Sk, int Hq, int Hkv, int D, int dtype, float scale) {
+  if (B <= 0 || Sq <= 0 || Sk <= 0 || Hq <= 0 || Hkv <= 0) {
+    set_error("sizes must be positive (B=%d Sq=%d Sk=%d Hq=%d Hkv=%d)", B, Sq, Sk, Hq, Hkv);
+    return SPA_EINVAL;
+  }
+  if (Hq % Hkv != 0) {
+    set_error("query heads (%d) must be a multiple of kv heads (%d)", Hq, Hkv);
+    return SPA_EINVAL;
+  }
+  if (!valid_head_dim(D)) {
+    set_error("head_dim must be 32, 64 or 128, got %d", D);
+    return SPA_EUNSUPPORTED;
+  }
+  if (dtype != SPA_DTYPE_F32 && dtype != SPA_DTYPE_BF16 && dtype != SPA_DTYPE_F16) {
+    set_error("unknown dtype %d", dtype);
+    return SPA_EINVAL;
+  }
+  if (!(scale > 0.f) || !isfinite(scale)) {
+    set_error("softmax scale must be positive and finite");
+    return SPA_EINVAL;
+  }
+  return SPA_OK;
+}
+
+int spa_attn_fwd(const spa_fwd_args* a) {
+  if (!a || !a->q || !a->k || !a->v || !a->lse) {
+    set_error("spa_attn_fwd: null pointer argument");
+    return SPA_EINVAL;
+  }
+  int rc = validate_common(a->B, a->Sq, a->Sk, a->Hq, a->Hkv, a->D, a->dtype, a->scale);
+  if (rc) return rc;
+  if (!a->out && !a->out_acc) {
+    set_error("spa_attn_fwd: at least one of out / out_acc is required");
+    return SPA_EINVAL;
+  }
+  if (a->merge_prev && !a->out_acc) {
+    set_error("spa_attn_fwd: merge_prev needs out_acc");
+    return SPA_EINVAL;
+  }
+  const bool tensor_core = a->dtype != SPA_DTYPE_F32 && a->D != 32 && !force_simt();
+  rc = tensor_core ? launch_fwd_sm100(a) : launch_fwd_simt(a);
+  if (rc == SPA_OK) note_launch(1);
+  return rc;
+}
+
+int spa_attn_bwd(const spa_bwd_args* a) {
+  if (!a || !a->q || !a->k || !a->v || !a->dout || !a->lse || !a->delta || !a->dq_acc || !a->dk ||
+      !a->dv) {
+    set_error("spa_attn_bwd: null pointer argument");
+    return SPA_EINVAL;
+  }
+  int rc = validate_common(a->B, a->Sq, a->Sk, a->Hq, a->Hkv, a->D, a->dtype, a->scale);
+  if (rc) return rc;
+  const bool tensor_core = a->dtype != SPA_DTYPE_F32 && a->D != 32 && !force_simt();
+  rc = tensor_core ? launch_bwd_sm100(a) : launch_bwd_simt(a);
+  if (rc == SPA_OK) note_launch(tensor_core ? 1 : 2);
+  return rc;
+}
+
+#define SPA_DISPATCH_T(dtype, ...)                                 \
+  switch (dtype) {                                                 \
+    case SPA_DTYPE_F32: { using T = float; __VA_ARGS__; } break;   \
+    case SPA_DTYPE_BF16: { using T = __nv_bfloat16; __VA_ARGS__; } break; \
+    case SPA_DTYPE_F16: { using T = __half; __VA_ARGS__; } break;  \
+    default: set_error("unknown dtype %d", dtype); return SPA_EINVAL; \
+  }
+
+int spa_bwd_delta(const void* out, int64_t o_sb, int64_t o_ss, int64_t o_sh, const void* dout,
+                  int64_t do_sb, int64_t do_ss, int64_t do_sh, float* delta, int32_t B, int32_t S,
+                  int32_t H, int32_t D, int32_t dtype, void* stream) {
+  if (!out || !dout || !delta || B <= 0 || S <= 0 || H <= 0 || !valid_head_dim(D)) {
+    set_error("spa_bwd_delta: bad argument");
+    return SPA_EINVAL;
+  }
+  const long long threads = (long long)B * S * H * (D / 4);
+  const int block = 256;
+  const long long grid = (threads + block - 1) / block;
+  SPA_DISPATCH_T(dtype, delta_kernel<T><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
+                            (const T*)out, o_sb, o_ss, o_sh, (const T*)dout, do_sb, do_ss, do_sh,
+                            delta, B, S, H, D));
+  int rc = check_launch("delta");
+  if (rc == SPA_OK) note_launch();
+  return rc;
+}
+
+int spa_merge(float* out_acc, float* lse, const void* block_out, int64_t bo_sb, int64_t bo_ss,
+              int64_t bo_sh, const float* block_lse, int32_t B, int32_t S, int32_t H, int32_t D,
+              int32_t dtype, void* stream) {
+  if (!out_acc || !lse || !block_out || !block_lse || B <= 0 || S <= 0 || H <= 0 ||
+      !valid_head_dim(D)) {
+    set_error("spa_merge: bad argument");
+    return SPA_EINVAL;
+  }
+  const long long threads = (long long)B * S * H * (D / 4);
+  const int block = 256;
+  const long long grid = (threads + block - 1) / block;
+  SPA_DISPATCH_T(dtype, merge_kernel<T><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
+                            out_acc, lse, (const T*)block_out, bo_sb, bo_ss, bo_sh, block_lse, B, S,
+                            H, D));
+  int rc = check_launch("merge");
+  if (rc == SPA_OK) note_launch();
+  return rc;
+}
+
+int spa_cast_from_f32(const float* src, void* dst, int64_t d_sb, int64_t d_ss, int64_t d_sh,
+                      int32_t B, int32_t S, int32_t H, int32_t D, int32_t dtype, float alpha,
+                      void* stream) {
+  if (!src || !dst || B <= 0 || S <= 0 || H <= 0 || !valid_head_dim(D)) {
+    set_error("spa_cast_from_f32: bad argument");
+    return SPA_EINVAL;
+  }
+  const long long threads = (long long)B * S * H * (D / 4);
+  const int block = 256;
+  const long long grid = (threads + block - 1) / block;
+  SPA_DISPATCH_T(dtype, cast_kernel<T><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
+                            src, (T*)dst, d_sb, d_ss, d_sh, B, S, H, D, alpha));
+  int rc = check_launch("cast");
+  if (rc == SPA_OK) note_launch();
+  return rc;
+}
+
+int spa_permute_rows(const void* src, void* dst, const int64_t n[4], const int64_t src_stride[4],
+                     const int64_t dst_stride[4], int64_t row_bytes, void* stream) {
+  if (!src || !dst || !n || !src_stride || !dst_stride || row_bytes <= 0 || (row_bytes & 15)) {
+    set_error("spa_permute_rows: bad argument (row_bytes must be a positive multiple of 16)");
+    return SPA_EINVAL;
+  }
+  if (((uintptr_t)src & 15) || ((uintptr_t)dst & 15)) {
+    set_error("spa_permute_rows: base pointers must be 16-byte aligned");
+    return SPA_EINVAL;
+  }
+  PermuteParams p;
+  int64_t rows = 1;
+  for (int i = 0; i < 4; ++i) {
+    if (n[i] <= 0 || (src_stride[i] & 15) || (dst_stride[i] & 15)) {
+      set_error("spa_permute_rows: extents must be positive and strides 16-byte multiples");
+      return SPA_EINVAL;
+    }
+    p.n[i] = n[i];
+    p.ss[i] = src_stride[i];
+    p.ds[i] = dst_stride[i];
+    rows *= n[i];
+  }
+  p.vec_per_row = row_bytes / 16;
+  p.total_vec = rows * p.vec_per_row;
+  const int block = 256;
+  // A few waves of 148 SMs x 8 resident blocks; the kernel grid-strides.
+  int64_t grid = (p.total_vec + block - 1) / block;
+  const int64_t cap = 148 * 8 * 4;
+  if (grid > cap) grid = cap;
+  permute_rows_kernel<<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>((const uint8_t*)src,
+                                                                          (uint8_t*)dst, p);
+  int rc = check_launch("permute_rows");
+  if (rc == SPA_OK) note_launch();
+  return rc;
+}
+
+}  // extern "C"

@@ -1,0 +1,31 @@
+// Internal declarations shared by the kernels and the C-ABI translation unit.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/spa.h"
+
+namespace spa {
+
+// Error text for spa_last_error(); thread-local.
+void set_error(const char* fmt, ...);
+
+// Device-global status word (4 ints) of the current device; allocated lazily,
+// zero while no bounded wait has ever given up.
+int* device_status_word();
+
+// Encode a 4-D TMA descriptor (dims D, S, H, B; 128-byte swizzle; box of
+// `box_rows` sequence rows by 64 two-byte elements). Returns 0 on success.
+int encode_rows_map(CUtensorMap* map, const void* ptr, int is_bf16, int D, int64_t S, int H, int B,
+                    int64_t stride_s, int64_t stride_h, int64_t stride_b, int box_rows);
+
+// Launchers (return a spa status code).
+int launch_fwd_sm100(const spa_fwd_args* a);
+int launch_bwd_sm100(const spa_bwd_args* a);
+int launch_fwd_simt(const spa_fwd_args* a);
+int launch_bwd_simt(const spa_bwd_args* a);
+
+inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+}  // namespace spa

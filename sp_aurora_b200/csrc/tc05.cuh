@@ -1,0 +1,245 @@
+// Thin inline-PTX wrappers for the Blackwell (sm_100a) primitives the attention
+// kernels use: mbarriers with BOUNDED waits, TMA tiled loads, tcgen05 tensor
+// memory allocation, tcgen05.mma (operands from shared memory), tcgen05.ld/st
+// and the fences that order the generic, async and tensor-core proxies.
+//
+// Every wait in this file gives up after a clock budget, records where it gave
+// up in a global status word and lets the kernel run to its normal exit (TMEM
+// freed, no trap), so that a protocol bug can never leave the GPU spinning.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace spa {
+
+// ---------------------------------------------------------------------------
+// Status word shared by all CTAs of a launch (device global memory, 4 ints):
+//   [0] error code (0 = ok)   [1] blockIdx.x   [2] site id   [3] iteration
+// ---------------------------------------------------------------------------
+enum : int { ST_OK = 0, ST_WAIT_TIMEOUT = 1 };
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Per-CTA view of the abort machinery.
+struct WaitCtx {
+  int* status;            // global status word (4 ints)
+  volatile int* cta_abort;  // shared-memory flag of this CTA
+};
+
+#ifndef SPA_WAIT_BUDGET_CYCLES
+#define SPA_WAIT_BUDGET_CYCLES (4000000000ll)  // about two seconds of SM clock
+#endif
+
+// Wait for `parity` of `bar`. Returns false (and flags the launch as failed)
+// when the budget runs out or when another CTA already flagged a failure, in
+// which case the caller must skip its work and fall through to the exit path.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w,
+                                          int site, int iter) {
+  if (*w.cta_abort) return false;
+  if (mbar_try_wait(bar, parity)) return true;
+  long long t0 = clock64();
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++spins & 0x3ff) == 0) {
+      if (*w.cta_abort) return false;
+      if (*reinterpret_cast<volatile int*>(w.status) != 0) {
+        *w.cta_abort = 1;
+        return false;
+      }
+      if (clock64() - t0 > SPA_WAIT_BUDGET_CYCLES) {
+        if (atomicCAS(w.status, 0, ST_WAIT_TIMEOUT) == 0) {
+          w.status[1] = blockIdx.x;
+          w.status[2] = site;
+          w.status[3] = iter;
+          __threadfence();
+        }
+        *w.cta_abort = 1;
+        return false;
+      }
+    }
+  }
+}
+
+// Whole-warp wait: every lane waits, then the warp agrees on one outcome so that
+// warp-collective tcgen05.ld/st that follow are never executed by a partial warp.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w,
+                                          int site, int iter) {
+  const bool ok = mbar_wait(bar, parity, w, site, iter);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// ---------------------------------------------------------------------------
+// TMA: tiled bulk tensor loads global -> shared, completion on an mbarrier.
+// The innermost coordinate times the element size must be a multiple of 16 B.
+// No cluster multicast anywhere in this library.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
+}
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* m, uint64_t* bar, int c0,
+                                            int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Tensor memory (TMEM) management. One warp allocates and the same warp frees.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                   smem_u32(dst_smem)),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+
+// ---------------------------------------------------------------------------
+// Descriptors.
+//
+// Shared-memory matrix descriptor (64 bit) for a 128-byte-swizzled tile whose
+// rows are 128 bytes (64 two-byte elements) and whose 8-row groups are 1024 B:
+//   bits  0-13 start address >> 4        bits 16-29 leading byte offset >> 4
+//   bits 32-45 stride byte offset >> 4   bits 46-47 descriptor version (1)
+//   bits 61-63 swizzle mode (2 = 128 B)
+// K-major operand  (rows = M or N, row bytes = K): SBO = bytes between 8-row
+//   groups (1024); LBO unused; advance K by 16 elements = +32 B.
+// MN-major operand (rows = K, row bytes = 64 elements of M or N): SBO = bytes
+//   between 8-row K groups (1024); LBO = bytes between successive 64-element
+//   column slabs; advance K by 16 rows = +2048 B.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes,
+                                                    uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+// Instruction descriptor for tcgen05.mma kind::f16 with fp32 accumulation:
+//   bits 4-5 D format (1 = f32); bits 7-9 A format, bits 10-12 B format
+//   (0 = f16, 1 = bf16); bit 15 A is MN-major; bit 16 B is MN-major;
+//   bits 17-22 N >> 3; bits 24-28 M >> 4.
+__host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16, bool a_mn, bool b_mn) {
+  return (1u << 4) | ((bf16 ? 1u : 0u) << 7) | ((bf16 ? 1u : 0u) << 10) |
+         ((a_mn ? 1u : 0u) << 15) | ((b_mn ? 1u : 0u) << 16) |
+         (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
+}
+
+// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrive on `bar` when every tcgen05 operation issued so far by this thread
+// has completed (implies tcgen05.fence::before_thread_sync).
+__device__ __forceinline__ void mma_commit(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+          smem_u32(bar))
+      : "memory");
+}
+
+// ---------------------------------------------------------------------------
+// TMEM <-> registers, shape 32x32b: lane i of the warp reads/writes TMEM lane
+// (32*(warp%4) + i), 32 consecutive 32-bit columns starting at taddr's column.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};" ::"r"(r[0]),
+      "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+      "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+      "r"(r[30]), "r"(r[31]), "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Byte offset of the 16-byte chunk holding elements [8*chunk, 8*chunk+8) of
+// row `row` inside a 128-byte-swizzled slab (rows of 64 two-byte elements).
+__device__ __forceinline__ uint32_t sw128_chunk_off(uint32_t row, uint32_t chunk) {
+  return row * 128u + ((chunk ^ (row & 7u)) << 4);
+}
+
+}  // namespace spa
