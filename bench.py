@@ -1,0 +1,336 @@
+"""Benchmark of the ring-attention hot path (forward + backward).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--seq S]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Workload: causal GQA kv-packed ring attention, bf16, B=1, total S=131072 split
+over the N ranks, 32 query heads / 8 kv heads, D=128, q/kv/dout ~ N(0, 0.5)
+from a fixed seed; one step = forward + backward through the public
+sp_aurora_kvpacked_func. Prints ONE JSON line on rank 0.
+
+FLOPs are the algorithmic ones: forward 4*B*Hq*S*S*D/2 (causal), backward 2.5x.
+`value` is the whole-job TFLOP/s with inputs resident in HBM; `e2e` repeats the
+measurement with pinned-host inputs copied in and a checksum read back each
+step. The CPU baseline and `--impl reference` time the CPU restatement of the
+reference's attention math (oracle/) on a bounded sample on the host cores.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+HQ, HKV, D, B = 32, 8, 128, 1
+DEFAULT_SEQ = 131072
+SIGMA = 0.5
+FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+
+
+def fwd_flops(seq, causal=True):
+    f = 4.0 * B * HQ * seq * seq * D
+    return f / 2 if causal else f
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return d, "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi SM clocks / throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_reference_sample(seq=4096, steps=1, threads=None):
+    """Forward+backward of the reference attention math on the host cores
+    (oracle port, fp32, the layout the reference is correct in), B/H/D of the
+    workload, causal, total sequence `seq`. Returns (TFLOP/s, seconds, threads)."""
+    from oracle import attention_oracle as orc
+    threads = threads or os.cpu_count() or 1
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(1234)
+    q = torch.randn(B, seq, HQ, D, generator=g) * SIGMA
+    k = torch.randn(B, seq, HKV, D, generator=g) * SIGMA
+    v = torch.randn(B, seq, HKV, D, generator=g) * SIGMA
+    dout = torch.randn(B, seq, HQ, D, generator=g) * SIGMA
+    best = None
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        out, lse = orc.attention_ref(q, k, v, None, True, dtype=torch.float32, block=512)
+        orc.attention_bwd_ref(dout, q, k, v, out, lse, None, True, dtype=torch.float32, block=512)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return 3.5 * fwd_flops(seq) / best / 1e12, best, threads
+
+
+def run_reference(args, rank, world):
+    """`--impl reference`: the reference's CPU attention math (oracle port) on
+    the host cores; rank 0 only, each step a bounded sample of the workload."""
+    if rank != 0:
+        return
+    sample_seq = 4096
+    threads = os.cpu_count() or 1
+    vals, secs = [], []
+    for i in range(args.warmup + args.steps):
+        tf, dt, _ = cpu_reference_sample(sample_seq, 1, threads)
+        if i >= args.warmup:
+            vals.append(tf)
+            secs.append(dt)
+    value = sum(vals) / len(vals)
+    sample = (f"oracle port (fp32 torch CPU) of the reference attention math, causal fwd+bwd, "
+              f"B={B} Hq={HQ} Hkv={HKV} D={D}, total S={sample_seq} (S^2-scaled sample of S={args.seq})")
+    line = {
+        "impl": "reference", "metric": "ring_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": 1e3 * sum(secs) / len(secs), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": workload_config(args, world),
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(args, world):
+    return {"workload": "cfg4: GQA kv-packed causal ring attention fwd+bwd (sp_aurora_kvpacked_func)",
+            "batch": B, "total_seq": args.seq, "seq_per_gpu": args.seq // world, "q_heads": HQ,
+            "kv_heads": HKV, "head_dim": D, "causal": True, "sigma": SIGMA,
+            "parallelism": f"ring{world}", "l2": "inputs exceed L2 (no flush needed)"}
+
+
+def make_inputs(seq_total, rank, world, device, pinned=False):
+    """Rank-local chunk of the global seeded tensors (chunk-seeded so results do
+    not depend on the number of ranks)."""
+    sl = seq_total // world
+    chunk = 4096
+    q = torch.empty(B, sl, HQ, D, dtype=torch.bfloat16)
+    kv = torch.empty(B, sl, 2, HKV, D, dtype=torch.bfloat16)
+    do = torch.empty(B, sl, HQ, D, dtype=torch.bfloat16)
+    for c0 in range(0, sl, chunk):
+        c1 = min(sl, c0 + chunk)
+        g = torch.Generator().manual_seed(4321 + (rank * sl + c0) // chunk)
+        q[:, c0:c1] = (torch.randn(B, c1 - c0, HQ, D, generator=g) * SIGMA).to(torch.bfloat16)
+        kv[:, c0:c1] = (torch.randn(B, c1 - c0, 2, HKV, D, generator=g) * SIGMA).to(torch.bfloat16)
+        do[:, c0:c1] = (torch.randn(B, c1 - c0, HQ, D, generator=g) * SIGMA).to(torch.bfloat16)
+    if pinned:
+        return q.pin_memory(), kv.pin_memory(), do.pin_memory()
+    return q.to(device), kv.to(device), do.to(device)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--seq", type=int, default=DEFAULT_SEQ)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import sp_aurora_b200 as spa
+    from sp_aurora_b200 import local_attn
+
+    assert torch.cuda.is_available(), "bench.py needs a GPU (there is no CPU path)"
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    group = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    assert args.seq % (world * 256) == 0
+
+    hq, hkv, hdo = make_inputs(args.seq, rank, world, device, pinned=True)
+    q, kv, dout = hq.to(device), hkv.to(device), hdo.to(device)
+    q.requires_grad_(True)
+    kv.requires_grad_(True)
+
+    def step(qt, kvt, dt):
+        qt.grad = None
+        kvt.grad = None
+        out = spa.sp_aurora_kvpacked_func(qt, kvt, causal=True, group=group)
+        out.backward(dt)
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step(q, kv, dout)
+    barrier()
+    spa.check_status()
+
+    # ---------------- timed region: inputs resident in HBM ----------------
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    local_attn.KERNEL_TIMERS = {}
+    launches0 = spa.launch_count()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step(q, kv, dout)
+    e1.record()
+    barrier()
+    launches = spa.launch_count() - launches0
+    ms = e0.elapsed_time(e1) / args.steps
+    timers = local_attn.KERNEL_TIMERS
+    local_attn.KERNEL_TIMERS = None
+    clocks = sampler.stop() if rank == 0 else None
+    kt = {k: [a.elapsed_time(b) for a, b in v] for k, v in timers.items()}
+    t = torch.tensor([ms], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    spa.check_status()
+
+    # ---------------- end to end: pinned host inputs, checksum read back ----------------
+    dq_, dkv_, ddo_ = torch.empty_like(q), torch.empty_like(kv), torch.empty_like(dout)
+    dq_.requires_grad_(True)
+    dkv_.requires_grad_(True)
+    host_res = torch.empty(3, dtype=torch.float32).pin_memory()
+
+    def e2e_step():
+        with torch.no_grad():
+            dq_.copy_(hq, non_blocking=True)
+            dkv_.copy_(hkv, non_blocking=True)
+            ddo_.copy_(hdo, non_blocking=True)
+        out = step(dq_, dkv_, ddo_)
+        res = torch.stack((out.float().sum(), dq_.grad.float().sum(), dkv_.grad.float().sum()))
+        host_res.copy_(res, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    f1.record()
+    barrier()
+    t = torch.tensor([f0.elapsed_time(f1) / args.steps], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item())
+
+    total_flops = 3.5 * fwd_flops(args.seq)
+    value = total_flops / (ms * 1e-3) / 1e12
+    peaks, peak_kind = load_peaks()
+    peak_sust = peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"])
+    peak_burst = peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])
+
+    if rank == 0:
+        # dominant kernel = backward; algorithmic FLOPs per launch = 2.5x forward of
+        # the blocks this rank computes per step, averaged over its launches
+        bwd_ms = kt.get("bwd", [])
+        fwd_ms = kt.get("fwd", [])
+        n_b = max(1, len(bwd_ms))
+        # rank 0 of a causal ring computes only its diagonal block each step
+        sl = args.seq // world
+        rank0_fwd = 4.0 * B * HQ * sl * sl * D / 2
+        bwd_flops_per_launch = 2.5 * rank0_fwd
+        avg_bwd = sum(bwd_ms) / n_b if bwd_ms else float("nan")
+        achieved = bwd_flops_per_launch / (avg_bwd * 1e-3) / 1e12 if bwd_ms else None
+        avg_fwd = sum(fwd_ms) / max(1, len(fwd_ms)) if fwd_ms else float("nan")
+        line = {
+            "metric": "ring_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "config": workload_config(args, world),
+            "tflops_per_gpu": value / world,
+            "pct_of_bf16_peak_burst": 100.0 * value / world / peak_burst,
+            "pct_of_bf16_peak_sustained": 100.0 * value / world / peak_sust,
+            "tokens_per_s": B * args.seq / (ms * 1e-3),
+            "roofline": {"bound": "tensor", "kernel": "attn_bwd_sm100_kernel<128,bf16>",
+                         "achieved": achieved, "peak": peak_sust, "unit": "TFLOP/s",
+                         "frac": (achieved / peak_sust) if achieved else None,
+                         "peak_source": f"{peak_kind} bf16_tflops_sustained", "traffic": None,
+                         "avg_launch_ms": avg_bwd, "launches_timed": len(bwd_ms),
+                         "fwd_kernel": {"avg_launch_ms": avg_fwd,
+                                        "achieved": (rank0_fwd / (avg_fwd * 1e-3) / 1e12) if fwd_ms else None}},
+            "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                    "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": int(world * (hq.numel() + hkv.numel() + hdo.numel()) * 2),
+                    "d2h_bytes_per_step": int(world * host_res.numel() * 4)},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            tf, secs, threads = cpu_reference_sample(4096, 1)
+            line["cpu_baseline"] = {
+                "value": tf, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                "sample": f"oracle port (fp32 torch CPU), causal fwd+bwd, same B/H/D, total S=4096, "
+                          f"{secs:.1f} s; S^2-scaled stand-in for S={args.seq}"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -19,6 +19,29 @@ from ._lib import BwdArgs, FwdArgs, check, lib, stream_ptr
 
 _SUPPORTED_D = (32, 64, 128)
 
+# Optional per-kernel timing: when set to a dict, every forward/backward kernel
+# call appends a (start, end) CUDA-event pair, recorded on the launching stream,
+# under "fwd" / "bwd". Used by the benchmark; None (default) records nothing.
+KERNEL_TIMERS = None
+
+
+class _Timed:
+    def __init__(self, name, device):
+        self.name, self.device = name, device
+
+    def __enter__(self):
+        if KERNEL_TIMERS is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.end = torch.cuda.Event(enable_timing=True)
+            self.start.record(torch.cuda.current_stream(self.device))
+        return self
+
+    def __exit__(self, *exc):
+        if KERNEL_TIMERS is not None:
+            self.end.record(torch.cuda.current_stream(self.device))
+            KERNEL_TIMERS.setdefault(self.name, []).append((self.start, self.end))
+        return False
+
 
 def check_unsupported_kwargs(dropout_p=0.0, window_size=(-1, -1), alibi_slopes=None, softcap=0.0):
     """The reference accepts and silently ignores these
@@ -98,7 +121,8 @@ def attn_fwd_step(q, k, v, softmax_scale: float, causal: bool, lse: torch.Tensor
     a.causal, a.causal_off, a.merge_prev = int(bool(causal)), int(causal_off), int(bool(merge_prev))
     a.scale = float(softmax_scale)
     a.stream = stream_ptr(q.device)
-    check(lib.spa_attn_fwd(C.byref(a)), "spa_attn_fwd")
+    with _Timed("fwd", q.device):
+        check(lib.spa_attn_fwd(C.byref(a)), "spa_attn_fwd")
 
 
 def flash_attn_forward(q, k, v, softmax_scale: Optional[float] = None, causal: bool = False,
@@ -159,7 +183,8 @@ def attn_bwd_step(q, k, v, dout, lse, delta, softmax_scale: float, causal: bool,
     a.causal, a.causal_off = int(bool(causal)), int(causal_off)
     a.scale = float(softmax_scale)
     a.stream = stream_ptr(q.device)
-    check(lib.spa_attn_bwd(C.byref(a)), "spa_attn_bwd")
+    with _Timed("bwd", q.device):
+        check(lib.spa_attn_bwd(C.byref(a)), "spa_attn_bwd")
 
 
 def cast_from_f32(src: torch.Tensor, dtype: torch.dtype, alpha: float = 1.0,

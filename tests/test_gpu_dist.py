@@ -1,0 +1,138 @@
+"""Multi-GPU parity tests (NCCL, one process per GPU): ring, Ulysses and hybrid
+attention, forward and backward, each rank compared with its slice of the
+full-sequence CPU oracle. Skipped when fewer than two GPUs are visible; the
+schedules themselves are also covered on CPU ranks in tests/test_host.py."""
+import os
+import socket
+import sys
+import traceback
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rand(shape, seed, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randn(*shape, generator=g) * std
+
+
+def _errs(pairs):
+    return [float((a.detach().cpu().double() - b).abs().max()) for a, b in pairs]
+
+
+def _worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    res = {}
+    try:
+        import sp_aurora_b200 as spa
+        from oracle import attention_oracle as orc
+        sl_of = lambda S: slice(rank * (S // world), (rank + 1) * (S // world))
+
+        # ---- ring: fp32 anchor (B2 S1024 H32 D64 causal at W=2) and bf16 GQA kv-packed
+        for tag, dtype, B, S, Hq, Hkv, D, causal, tol in (
+                ("ring_fp32", torch.float32, 2, 1024, 32, 32, 64, True, 1e-4),
+                ("ring_bf16_gqa", torch.bfloat16, 1, 2048, 8, 2, 128, True, 2e-2),
+                ("ring_bf16_noncausal", torch.bfloat16, 1, 1024, 4, 4, 128, False, 2e-2)):
+            q = _rand((B, S, Hq, D), 1).to(dtype)
+            kv = _rand((B, S, 2, Hkv, D), 2).to(dtype)
+            do = _rand((B, S, Hq, D), 3).to(dtype)
+            ro, rl = orc.attention_ref(q, kv[:, :, 0], kv[:, :, 1], None, causal)
+            rdq, rdk, rdv = orc.attention_bwd_ref(do, q, kv[:, :, 0], kv[:, :, 1], ro, rl, None, causal)
+            sl = sl_of(S)
+            ql = q[:, sl].to(dev).requires_grad_(True)
+            kvl = kv[:, sl].to(dev).requires_grad_(True)
+            out, lse, _ = spa.sp_aurora_kvpacked_func(ql, kvl, causal=causal, return_attn_probs=True)
+            out.backward(do[:, sl].to(dev))
+            spa.check_status()
+            e = _errs([(out, ro[:, sl]), (ql.grad, rdq[:, sl]), (kvl.grad[:, :, 0], rdk[:, sl]),
+                       (kvl.grad[:, :, 1], rdv[:, sl])])
+            el = _errs([(lse, rl[:, :, sl])])[0]
+            gmax = max(1.0, float(rdv.abs().max()) / 4)
+            res[tag] = (max(e[:1]) <= tol and max(e[1:]) <= tol * gmax and el <= 1e-3, e, el)
+
+        # ---- Ulysses (non-causal and causal), B=2 exercises the unpack kernels
+        for tag, B, S, Hq, Hkv, D, causal in (("uly_b2", 2, 1024, 8, 8, 128, False),
+                                              ("uly_gqa_causal", 1, 1024, 8, 4, 128, True)):
+            q = _rand((B, S, Hq, D), 4).bfloat16()
+            k = _rand((B, S, Hkv, D), 5).bfloat16()
+            v = _rand((B, S, Hkv, D), 6).bfloat16()
+            do = _rand((B, S, Hq, D), 7).bfloat16()
+            ro, rl = orc.attention_ref(q, k, v, None, causal)
+            rdq, rdk, rdv = orc.attention_bwd_ref(do, q, k, v, ro, rl, None, causal)
+            sl = sl_of(S)
+            ql, kl, vl = (t[:, sl].to(dev).requires_grad_(True) for t in (q, k, v))
+            out, lse, _ = spa.ulysses_flash_attn_func(ql, kl, vl, causal=causal, return_attn_probs=True)
+            out.backward(do[:, sl].to(dev))
+            spa.check_status()
+            e = _errs([(out, ro[:, sl]), (ql.grad, rdq[:, sl]), (kl.grad, rdk[:, sl]), (vl.grad, rdv[:, sl])])
+            el = _errs([(lse, rl[:, :, sl])])[0]
+            gmax = max(1.0, float(rdv.abs().max()) / 4)
+            res[tag] = (max(e[:1]) <= 2e-2 and max(e[1:]) <= 2e-2 * gmax and el <= 1e-3, e, el)
+
+        # ---- all-to-all bit exactness on the GPU (pack kernel + NCCL + unpack kernel)
+        x = (torch.arange(2 * 64 * 4 * 64, dtype=torch.float32).view(2, 64, 4, 64) + 1e6 * rank).to(dev)
+        ins = [(torch.arange(2 * 64 * 4 * 64, dtype=torch.float32).view(2, 64, 4, 64) + 1e6 * r)
+               for r in range(world)]
+        y = spa.all_to_all_4D(x, 2, 1)
+        z = spa.all_to_all_4D(y, 1, 2)
+        want = orc.all_to_all_4d_ref(ins, 2, 1)[rank]
+        res["a2a_exact"] = (bool(torch.equal(y.cpu(), want) and torch.equal(z, x)), [], 0.0)
+
+        # ---- hybrid: Ulysses degree `world`, ring degree 1, and U=1 x R=world, qkv-packed
+        for tag, U, R in (("hyb_u", world, 1), ("hyb_r", 1, world)):
+            spa.destroy_seq_parallel_pg()
+            spa.set_seq_parallel_pg(U, R, rank, world)
+            B, S, H, D = 1, 1024, 4, 128
+            qkv = _rand((B, S, 3, H, D), 8).bfloat16()
+            ro, rl = orc.attention_ref(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], None, True)
+            sl = sl_of(S)
+            mod = spa.LongContextAttentionQKVPacked()
+            out, lse, _ = mod(qkv[:, sl].to(dev), causal=True, return_attn_probs=True)
+            spa.check_status()
+            e = _errs([(out, ro[:, sl])])
+            el = _errs([(lse, rl[:, :, sl])])[0]
+            res[tag] = (e[0] <= 2e-2 and el <= 1e-3, e, el)
+        spa.destroy_seq_parallel_pg()
+    except Exception:  # noqa: BLE001
+        res["error"] = traceback.format_exc()
+    ret[rank] = res
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.fixture(scope="module")
+def results():
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    world = 4 if n >= 4 else 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    out = {r: dict(ret[r]) for r in range(world)}
+    for r in out:
+        assert "error" not in out[r], out[r]["error"]
+    return out
+
+
+@pytest.mark.parametrize("tag", ["ring_fp32", "ring_bf16_gqa", "ring_bf16_noncausal", "uly_b2",
+                                 "uly_gqa_causal", "a2a_exact", "hyb_u", "hyb_r"])
+def test_multi_gpu_parity(results, tag):
+    for r, res in results.items():
+        ok, errs, el = res[tag]
+        assert ok, f"rank {r} {tag}: errs {errs} lse {el}"

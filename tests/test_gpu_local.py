@@ -1,0 +1,178 @@
+"""GPU parity tests of the per-device kernels against the CPU oracle.
+
+Tolerances (max-abs), as the build's parity contract states them:
+  bf16/fp16: out, dq, dk, dv <= 2e-2 ; fp32: <= 1e-4 ; lse <= 1e-3.
+Everything is called through the C-ABI library (ctypes)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+TOL = {torch.float32: 1e-4, torch.bfloat16: 2e-2, torch.float16: 2e-2}
+LSE_TOL = 1e-3
+
+
+@pytest.fixture(scope="module")
+def spa():
+    assert torch.cuda.is_available(), "GPU tests need a CUDA device"
+    import sp_aurora_b200 as m
+    return m
+
+
+def _rand(shape, dtype, seed, std=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * std).to(dtype)
+
+
+def _check_fwd(spa, B, Sq, Sk, Hq, Hkv, D, dtype, causal, seed=0):
+    q = _rand((B, Sq, Hq, D), dtype, seed)
+    k = _rand((B, Sk, Hkv, D), dtype, seed + 1)
+    v = _rand((B, Sk, Hkv, D), dtype, seed + 2)
+    out, lse = spa.flash_attn_forward(q.cuda(), k.cuda(), v.cuda(), None, causal)
+    spa.check_status()
+    ref_out, ref_lse = orc.attention_ref(q, k, v, None, causal)
+    eo = (out.cpu().double() - ref_out).abs().max().item()
+    el = (lse.cpu().double() - ref_lse).abs().max().item()
+    assert eo <= TOL[dtype], f"out err {eo}"
+    assert el <= LSE_TOL, f"lse err {el}"
+    return q, k, v, out, lse, ref_out, ref_lse
+
+
+def _check_bwd(spa, q, k, v, out, lse, ref_out, ref_lse, dtype, causal, seed=0):
+    dout = _rand(tuple(q.shape), dtype, seed + 3)
+    dq, dk, dv = spa.flash_attn_backward(dout.cuda(), q.cuda(), k.cuda(), v.cuda(), out, lse, None, causal)
+    spa.check_status()
+    rdq, rdk, rdv = orc.attention_bwd_ref(dout, q, k, v, ref_out, ref_lse, None, causal)
+    for name, got, want in (("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
+        err = (got.cpu().double() - want).abs().max().item()
+        scale = max(1.0, want.abs().max().item() / 4)     # gradients of O(10) keep relative meaning
+        assert err <= TOL[dtype] * scale, f"{name} err {err} (max |ref| {want.abs().max().item()})"
+
+
+# fp32 runs on the CUDA-core kernel: reference-test shapes (D 32/64/128, ragged, GQA)
+FP32_CASES = [
+    (1, 128, 128, 2, 2, 64, True), (1, 96, 160, 2, 2, 32, False), (2, 200, 200, 1, 1, 128, True),
+    (1, 64, 64, 3, 3, 64, False), (2, 130, 77, 4, 2, 64, False), (1, 257, 257, 4, 1, 128, True),
+]
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D,causal", FP32_CASES)
+def test_fp32_forward_backward(spa, B, Sq, Sk, Hq, Hkv, D, causal):
+    r = _check_fwd(spa, B, Sq, Sk, Hq, Hkv, D, torch.float32, causal)
+    _check_bwd(spa, *r, torch.float32, causal)
+
+
+# bf16 / fp16 run on the tcgen05 kernels
+TC_CASES = [
+    (1, 128, 128, 1, 1, 128, False), (1, 256, 256, 2, 2, 128, True), (2, 384, 384, 4, 2, 128, True),
+    (1, 512, 512, 4, 1, 128, False), (1, 300, 300, 2, 2, 128, True), (1, 130, 333, 2, 1, 128, False),
+    (1, 1024, 1024, 2, 2, 128, True), (1, 64, 64, 2, 2, 128, True), (2, 256, 256, 2, 2, 64, True),
+    (1, 200, 200, 4, 2, 64, False),
+]
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D,causal", TC_CASES)
+def test_bf16_forward_backward(spa, B, Sq, Sk, Hq, Hkv, D, causal):
+    r = _check_fwd(spa, B, Sq, Sk, Hq, Hkv, D, torch.bfloat16, causal)
+    _check_bwd(spa, *r, torch.bfloat16, causal)
+
+
+@pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D,causal", TC_CASES[:4])
+def test_fp16_forward_backward(spa, B, Sq, Sk, Hq, Hkv, D, causal):
+    r = _check_fwd(spa, B, Sq, Sk, Hq, Hkv, D, torch.float16, causal)
+    _check_bwd(spa, *r, torch.float16, causal)
+
+
+def test_golden_fixtures_on_gpu(spa, golden_dir):
+    """The reference's own outputs (fp32) reproduced by the CUDA path."""
+    gd = np.load(os.path.join(golden_dir, "local_attention.npz"))
+    for name in ("c0", "c1", "c2", "c3"):
+        B, H, Sq, Sk, D, causal = [int(x) for x in gd[f"{name}_meta"]]
+        q, k, v = (torch.from_numpy(gd[f"{name}_{t}"]).cuda() for t in "qkv")
+        out, lse = spa.flash_attn_forward(q, k, v, D ** -0.5, bool(causal))
+        assert (out.cpu() - torch.from_numpy(gd[f"{name}_out"])).abs().max() <= 1e-4
+        assert (lse.cpu() - torch.from_numpy(gd[f"{name}_lse"])).abs().max() <= 1e-3
+    o1, o2 = torch.from_numpy(gd["m_out1"]).cuda(), torch.from_numpy(gd["m_out2"]).cuda()
+    l1, l2 = torch.from_numpy(gd["m_lse1"]).cuda(), torch.from_numpy(gd["m_lse2"]).cuda()
+    out, lse = spa.update_out_and_lse(None, None, o1, l1)
+    out, lse = spa.update_out_and_lse(out, lse, o2, l2)
+    assert (out.cpu() - torch.from_numpy(gd["m_out"])).abs().max() <= 1e-5
+    assert (lse.cpu() - torch.from_numpy(gd["m_lse"])).abs().max() <= 1e-5
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_fused_merge_equals_full_attention(spa, dtype):
+    """Two key blocks through the fused merge epilogue == one call over all keys."""
+    from sp_aurora_b200.local_attn import attn_fwd_step
+    B, S, H, D = 1, 256, 2, 128
+    q, k, v = (_rand((B, S, H, D), dtype, s).cuda() for s in (1, 2, 3))
+    lse = torch.empty((B, H, S), dtype=torch.float32, device="cuda")
+    acc = torch.empty((B, S, H, D), dtype=torch.float32, device="cuda")
+    out = torch.empty((B, S, H, D), dtype=dtype, device="cuda")
+    attn_fwd_step(q, k[:, :128], v[:, :128], D ** -0.5, False, lse, out_acc=acc)
+    attn_fwd_step(q, k[:, 128:], v[:, 128:], D ** -0.5, False, lse, out=out, out_acc=acc, merge_prev=True)
+    spa.check_status()
+    ref_out, ref_lse = orc.attention_ref(q.cpu(), k.cpu(), v.cpu(), None, False)
+    assert (out.cpu().double() - ref_out).abs().max() <= TOL[dtype]
+    assert (lse.cpu().double() - ref_lse).abs().max() <= LSE_TOL
+
+
+def test_causal_offset_rows_without_keys(spa):
+    from sp_aurora_b200.local_attn import attn_fwd_step
+    B, S, H, D = 1, 256, 1, 128
+    q, k, v = (_rand((B, S, H, D), torch.bfloat16, s).cuda() for s in (4, 5, 6))
+    lse = torch.empty((B, H, S), dtype=torch.float32, device="cuda")
+    out = torch.empty_like(q)
+    attn_fwd_step(q, k, v, D ** -0.5, True, lse, out=out, causal_off=-130)
+    spa.check_status()
+    ref_out, ref_lse = orc.attention_ref(q.cpu(), k.cpu(), v.cpu(), None, True, causal_off=-130)
+    assert torch.isinf(lse[0, 0, :130]).all() and (out[0, :130] == 0).all()
+    assert (out.cpu().double() - ref_out).abs().max() <= 2e-2
+    assert (lse.cpu().double()[0, 0, 130:] - ref_lse[0, 0, 130:]).abs().max() <= LSE_TOL
+
+
+def test_packed_views_equal_separate_tensors(spa):
+    """kv[:, :, 0] / qkv[:, :, i] views are consumed in place (strided TMA)."""
+    B, S, H, D = 1, 256, 2, 128
+    qkv = _rand((B, S, 3, H, D), torch.bfloat16, 9).cuda()
+    o1, l1 = spa.flash_attn_forward(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], None, True)
+    o2, l2 = spa.flash_attn_forward(qkv[:, :, 0].contiguous(), qkv[:, :, 1].contiguous(),
+                                    qkv[:, :, 2].contiguous(), None, True)
+    assert torch.equal(o1, o2) and torch.equal(l1, l2)
+
+
+def test_strided_copy_bit_exact(spa):
+    from sp_aurora_b200.all_to_all import strided_copy
+    x = torch.arange(2 * 6 * 4 * 3 * 64, dtype=torch.float32).view(2, 6, 4, 3, 64).to(torch.bfloat16).cuda()
+    src = x.permute(2, 0, 1, 3, 4)
+    dst = torch.empty(src.shape, dtype=x.dtype, device="cuda")
+    strided_copy(dst, src)
+    assert torch.equal(dst, src.contiguous())
+
+
+def test_large_shape_against_cuda_core_kernel(spa):
+    """S = 4096, GQA, causal: tensor-core kernels vs the fp32 CUDA-core kernels
+    on the same bf16 data (size-independent cross-check, both on the GPU), plus a
+    CPU oracle spot check on a slice of the rows."""
+    B, S, Hq, Hkv, D = 1, 4096, 8, 2, 128
+    dt = torch.bfloat16
+    q, k, v, dout = (_rand(sh, dt, s, 1.0).cuda() for sh, s in (
+        ((B, S, Hq, D), 1), ((B, S, Hkv, D), 2), ((B, S, Hkv, D), 3), ((B, S, Hq, D), 4)))
+    out, lse = spa.flash_attn_forward(q, k, v, None, True)
+    dq, dk, dv = spa.flash_attn_backward(dout, q, k, v, out, lse, None, True)
+    spa.check_status()
+    o32, l32 = spa.flash_attn_forward(q.float(), k.float(), v.float(), None, True)
+    g32 = spa.flash_attn_backward(dout.float(), q.float(), k.float(), v.float(), o32, l32, None, True)
+    assert (out.float() - o32).abs().max() <= 2e-2
+    assert (lse - l32).abs().max() <= 1e-3
+    for got, want in zip((dq, dk, dv), g32):
+        assert (got.float() - want).abs().max() <= 2e-2 * max(1.0, want.abs().max().item() / 4)
+    rows = slice(3000, 3128)
+    ro, rl = orc.attention_ref(q[:, rows].cpu(), k.cpu(), v.cpu(), None, True, causal_off=3000)
+    assert (out[:, rows].cpu().double() - ro).abs().max() <= 2e-2
+    assert (lse[:, :, rows].cpu().double() - rl).abs().max() <= 1e-3
