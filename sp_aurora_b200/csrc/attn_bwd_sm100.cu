@@ -18,8 +18,12 @@
 // sp_aurora/intel_flash_attn.py:129 is a stub); formulas as in the manual
 // backward of sp_aurora/intel_ulysses_attn.py:403-426.
 //
-// CTA = 6 warps: 0-3 compute group (thread = key row / dQ^T lane), 4 = TMA
-// producer, 5 = MMA issuer and TMEM owner.
+// CTA = 14 warps:
+//   warps 0-3   compute group A: key row per thread, query columns  0-31
+//   warps 4-7   compute group B: key row per thread, query columns 32-63
+//   warps 8-11  dQ drain group: head-dim lane per thread; TMEM -> shared memory
+//               (fp32 [64 queries][D]) -> one TMA reduce-add into the dq accumulator
+//   warp  12    TMA producer          warp 13  MMA issuer and TMEM owner
 // TMEM columns: S^T [0,64) dP^T [64,128) dV [128,128+D) dK [256,256+D) dQ^T [384,448).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -35,7 +39,8 @@ namespace {
 
 constexpr int kTileKV = 128;
 constexpr int kTileQ = 64;
-constexpr int kThreads = 192;
+constexpr int kThreads = 448;
+constexpr int kWarpTma = 12, kWarpMma = 13;
 constexpr int kStages = 3;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -68,9 +73,10 @@ struct BwdSmem {
   static constexpr int kStageOff = kVOff + kKVTile;
   static constexpr int kPOff = kStageOff + kStages * kStageBytes;
   static constexpr int kDSOff = kPOff + kPBytes;
-  static constexpr int kRowOff = kDSOff + kPBytes;           // lse2/delta [2][2][64] floats
+  static constexpr int kDQOff = kDSOff + kPBytes;            // dQ staging fp32 [64][D]
+  static constexpr int kRowOff = kDQOff + kTileQ * D * 4;    // lse2/delta [2][2][64] floats
   static constexpr int kBarOff = kRowOff + 2 * 2 * 64 * 4;
-  static constexpr int kNumBars = 1 + 2 * kStages + 6;
+  static constexpr int kNumBars = 1 + 2 * kStages + 8;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
 };
 
@@ -92,7 +98,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v,
-                      const __grid_constant__ CUtensorMap tm_do, const BwdParams p) {
+                      const __grid_constant__ CUtensorMap tm_do,
+                      const __grid_constant__ CUtensorMap tm_dq, const BwdParams p) {
   using L = BwdSmem<D>;
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   extern __shared__ uint8_t smem_raw[];
@@ -108,6 +115,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint64_t* mma_done = pds_full + 1;
   uint64_t* dq_free = mma_done + 1;
   uint64_t* row_ready = dq_free + 1;
+  uint64_t* stage_full = row_ready + 1;
+  uint64_t* stage_free = stage_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* row_buf = reinterpret_cast<float*>(smem + L::kRowOff);  // [buf][lse2|delta][64]
@@ -144,15 +153,17 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       mbar_init(&qdo_empty[i], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(sdp_free, 128);
-    mbar_init(pds_full, 128);
+    mbar_init(sdp_free, 256);
+    mbar_init(pds_full, 256);
     mbar_init(mma_done, 1);
     mbar_init(dq_free, 128);
     mbar_init(row_ready, 128);
+    mbar_init(stage_full, 128);
+    mbar_init(stage_free, 1);
     fence_mbar_init();
     fence_proxy_async_smem();
   }
-  if (warp == 5) {
+  if (warp == kWarpMma) {
     tmem_alloc(tmem_slot, 512);
     tmem_relinquish();
   }
@@ -162,7 +173,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   const uint32_t tmem_base = *tmem_slot;
   WaitCtx wc{p.status, cta_abort};
 
-  if (warp == 4) {
+  if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA
     if (lane == 0 && n_it > 0) {
       tma_prefetch_desc(&tm_q);
@@ -188,7 +199,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA
     if (lane == 0 && n_it > 0) {
       constexpr uint32_t idesc_sdp = make_idesc(128, kTileQ, kBf16, false, false);
@@ -266,24 +277,73 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
         mma_commit(&qdo_empty[slot]);
       }
     }
+  } else if (warp >= 8) {
+    // ---------------------------------------------------------------- drain
+    // dQ^T tile (TMEM lanes = head dim, columns = queries) -> shared memory as
+    // fp32 [query][head dim] -> one bulk tensor reduce-add into dq_acc.
+    const int quad = warp & 3;
+    const int d = quad * 32 + lane;
+    const int tid = threadIdx.x - 8 * 32;
+    const uint32_t t_dq = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kColDQ;
+    float* stage = reinterpret_cast<float*>(smem + L::kDQOff);
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      ok = warp_wait(mma_done, it & 1, wc, 400, it);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t v0[32], v1[32];
+      tmem_ld32(t_dq, v0);
+      tmem_ld32(t_dq + 32, v1);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(dq_free);
+      // staging buffer must have been read by the previous reduce
+      ok = warp_wait(stage_free, (it & 1) ^ 1, wc, 401, it);
+      if (!ok) break;
+      if (d < D) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          stage[i * D + d] = __uint_as_float(v0[i]) * p.scale;
+          stage[(32 + i) * D + d] = __uint_as_float(v1[i]) * p.scale;
+        }
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(stage_full);
+      if (tid == 0) {
+        ok = mbar_wait(stage_full, it & 1, wc, 402, it);
+        if (ok) {
+          const int hq = g * G + it / n_q;
+          const int q0 = (i_start + it % n_q) * kTileQ;
+          tma_reduce_add_4d(&tm_dq, stage, 0, q0, hq, b);
+          bulk_commit_group();
+          bulk_wait_read_all();
+          mbar_arrive(stage_free);
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+    }
+    if (tid == 0) bulk_wait_all();
   } else {
     // -------------------------------------------------------------- compute
+    const int grp = warp >> 2;               // 0: query columns 0-31, 1: columns 32-63
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;          // key row in tile, and dQ^T lane (head-dim index)
+    const int r = quad * 32 + lane;          // key row in tile
     const int kidx = kv0 + r;
+    const int c_base = grp * 32;
     const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_field + kColS;
-    const uint32_t t_dp = tmem_base + lane_field + kColDP;
+    const uint32_t t_s = tmem_base + lane_field + kColS + c_base;
+    const uint32_t t_dp = tmem_base + lane_field + kColDP + c_base;
     const uint32_t t_dv = tmem_base + lane_field + kColDV;
     const uint32_t t_dk = tmem_base + lane_field + kColDK;
-    const uint32_t t_dq = tmem_base + lane_field + kColDQ;
     uint8_t* p_row = smem + L::kPOff;
     uint8_t* ds_row = smem + L::kDSOff;
     const bool key_ok = kidx < p.Sk;
     bool ok = true;
 
-    // Row statistics of a query tile: threads 0-63 fetch lse (pre-multiplied by
-    // log2 e), threads 64-127 fetch delta. +inf lse makes out-of-range rows give P = 0.
+    // Row statistics of a query tile, fetched by group A: threads 0-63 lse
+    // (pre-multiplied by log2 e), threads 64-127 delta. +inf lse makes
+    // out-of-range rows give P = 0.
     auto fetch_rowstat = [&](int it) -> float {
       const int hq = g * G + it / n_q;
       const int q0 = (i_start + it % n_q) * kTileQ;
@@ -293,66 +353,44 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       if (r < 64) return qi < p.Sq ? p.lse[idx] * kLog2e : INFINITY;
       return qi < p.Sq ? p.delta[idx] : 0.f;
     };
-    // dQ^T drain of iteration `it`: thread = head-dim index, columns = queries.
-    auto drain_dq = [&](int it) {
-      const int hq = g * G + it / n_q;
-      const int q0 = (i_start + it % n_q) * kTileQ;
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        uint32_t v[32];
-        tmem_ld32(t_dq + c * 32, v);
-        tmem_ld_wait();
-        if (r < D) {
-          float* base = p.dq_acc + (((size_t)b * p.Sq + q0 + c * 32) * p.Hq + hq) * D + r;
-          const int nvalid = min(32, p.Sq - (q0 + c * 32));
-#pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (i < nvalid) atomicAdd(base + (size_t)i * p.Hq * D, __uint_as_float(v[i]) * p.scale);
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(dq_free);
-    };
 
-    if (n_it > 0) {
+    if (n_it > 0 && grp == 0) {
       row_buf[(0 * 2 + (r >> 6)) * 64 + (r & 63)] = fetch_rowstat(0);
       mbar_arrive(row_ready);
     }
 
     for (int it = 0; it < n_it; ++it) {
       float next_stat = 0.f;
-      if (it + 1 < n_it) next_stat = fetch_rowstat(it + 1);
+      if (grp == 0 && it + 1 < n_it) next_stat = fetch_rowstat(it + 1);
 
       ok = warp_wait(sdp_full, it & 1, wc, 300, it);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sr[64], dpr[64];
+      uint32_t sr[32], dpr[32];
       tmem_ld32(t_s, sr);
-      tmem_ld32(t_s + 32, sr + 32);
       tmem_ld32(t_dp, dpr);
-      tmem_ld32(t_dp + 32, dpr + 32);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(sdp_free);
 
-      // Row statistics of this iteration are in shared memory once all 128
-      // threads of the group have arrived (bounded, unlike a bar.sync).
+      // Row statistics of this iteration are in shared memory once group A's
+      // 128 threads have arrived (bounded, unlike a bar.sync).
       ok = warp_wait(row_ready, it & 1, wc, 305, it);
       if (!ok) break;
-      const float* lse2 = row_buf + ((it & 1) * 2 + 0) * 64;
-      const float* dlt = row_buf + ((it & 1) * 2 + 1) * 64;
+      const float* lse2 = row_buf + ((it & 1) * 2 + 0) * 64 + c_base;
+      const float* dlt = row_buf + ((it & 1) * 2 + 1) * 64 + c_base;
       const int q0 = (i_start + it % n_q) * kTileQ;
       // Visible iff kidx <= q + off  <=>  column c >= kidx - off - q0.
       int c_min = 0;
       if (p.causal) {
-        const long long cm = (long long)kidx - p.causal_off - q0;
-        c_min = (int)max(0ll, min(cm, 64ll));
+        const long long cm = (long long)kidx - p.causal_off - q0 - c_base;
+        c_min = (int)max(0ll, min(cm, 32ll));
       }
-      if (!key_ok) c_min = 64;
+      if (!key_ok) c_min = 32;
 
-      uint32_t pp[32], dsp[32];
+      uint32_t pp[16], dsp[16];
 #pragma unroll
-      for (int c4 = 0; c4 < 16; ++c4) {
+      for (int c4 = 0; c4 < 8; ++c4) {
         const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
         const float4 d4 = *reinterpret_cast<const float4*>(dlt + 4 * c4);
         const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
@@ -373,56 +411,52 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
 
       if (it > 0) {
-        // dV/dK/dQ MMAs of the previous iteration have read P^T/dS^T and
-        // produced dQ^T(it-1).
+        // dV/dK/dQ MMAs of the previous iteration have finished reading P^T/dS^T.
         ok = warp_wait(mma_done, (it - 1) & 1, wc, 310, it);
         if (!ok) break;
         tc_fence_after();
       }
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const uint32_t off = sw128_chunk_off(r, c);
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t off = sw128_chunk_off(r, grp * 4 + c);
         *reinterpret_cast<uint4*>(p_row + off) =
             make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
         *reinterpret_cast<uint4*>(ds_row + off) =
             make_uint4(dsp[4 * c], dsp[4 * c + 1], dsp[4 * c + 2], dsp[4 * c + 3]);
       }
-      if (it + 1 < n_it) {
+      if (grp == 0 && it + 1 < n_it) {
         row_buf[(((it + 1) & 1) * 2 + (r >> 6)) * 64 + (r & 63)] = next_stat;
         mbar_arrive(row_ready);
       }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(pds_full);
-
-      if (it > 0) drain_dq(it - 1);
     }
 
     if (ok && n_it > 0) {
       ok = warp_wait(mma_done, (n_it - 1) & 1, wc, 320, n_it);
-      if (ok) {
-        tc_fence_after();
-        drain_dq(n_it - 1);
-      }
+      if (ok) tc_fence_after();
     }
 
     // ------------------------------------------------------------- epilogue
+    // dV and dK rows: group A writes head-dim columns [0, D/2), group B the rest.
     if (ok) {
       const size_t row_off = (((size_t)b * p.Sk + kidx) * p.Hkv + g) * D;
+      constexpr int kHalfChunks = D / 64;  // 32-column chunks per group
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const uint32_t taddr = which == 0 ? t_dv : t_dk;
-        const float mul = which == 0 ? 1.f : p.scale;
         void* dst_base = which == 0 ? p.dv : p.dk;
 #pragma unroll
-        for (int c = 0; c < D / 32; ++c) {
+        for (int cc = 0; cc < kHalfChunks; ++cc) {
+          const int c = grp * kHalfChunks + cc;
           float o[32];
           if (n_it > 0) {
             uint32_t v[32];
             tmem_ld32(taddr + c * 32, v);
             tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * mul;
+            for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * (which == 0 ? 1.f : p.scale);
           } else {
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = 0.f;
@@ -464,7 +498,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
     __syncthreads();
   }
-  if (warp == 5) {
+  if (warp == kWarpMma) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -473,7 +507,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
 template <int D, typename T>
 int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
   using L = BwdSmem<D>;
-  CUtensorMap tq, tk, tv, tdo;
+  CUtensorMap tq, tk, tv, tdo, tdq;
+  if (encode_f32_rows_map(&tdq, a->dq_acc, D, a->Sq, a->Hq, a->B, kTileQ)) return SPA_ECUDA;
   if (encode_rows_map(&tq, a->q, is_bf16, D, a->Sq, a->Hq, a->B, a->q_ss, a->q_sh, a->q_sb, kTileQ))
     return SPA_ECUDA;
   if (encode_rows_map(&tdo, a->dout, is_bf16, D, a->Sq, a->Hq, a->B, a->do_ss, a->do_sh, a->do_sb,
@@ -508,7 +543,7 @@ int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
     set_error("bwd grid out of range");
     return SPA_EINVAL;
   }
-  kern<<<(unsigned)grid, kThreads, smem_bytes, (cudaStream_t)a->stream>>>(tq, tk, tv, tdo, p);
+  kern<<<(unsigned)grid, kThreads, smem_bytes, (cudaStream_t)a->stream>>>(tq, tk, tv, tdo, tdq, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("bwd sm100 launch: %s", cudaGetErrorString(e));

@@ -20,6 +20,11 @@ int* device_status_word();
 int encode_rows_map(CUtensorMap* map, const void* ptr, int is_bf16, int D, int64_t S, int H, int B,
                     int64_t stride_s, int64_t stride_h, int64_t stride_b, int box_rows);
 
+// 4-D TMA descriptor over a contiguous fp32 [B,S,H,D] tensor (dims D, S, H, B; no
+// swizzle; box of `box_rows` sequence rows by D), used for bulk reduce-add.
+int encode_f32_rows_map(CUtensorMap* map, const void* ptr, int D, int64_t S, int H, int B,
+                        int box_rows);
+
 // Launchers (return a spa status code).
 int launch_fwd_sm100(const spa_fwd_args* a);
 int launch_bwd_sm100(const spa_bwd_args* a);
