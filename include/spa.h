@@ -122,6 +122,53 @@ typedef struct spa_bwd_args {
 int spa_attn_bwd(const spa_bwd_args* args);
 
 /*
+ * Backward pass for callers that cannot allocate device memory.
+ *
+ * No counterpart in the reference. Who needs it: code that runs where every
+ * byte of the GPU already belongs to someone else's pool, or that may not call
+ * into the CUDA allocator at all (a fixed-budget service, a thread that must
+ * not block on allocator locks). spa_attn_bwd makes such a caller bring two
+ * scratch buffers (delta and the fp32 dq accumulator); this entry keeps them in
+ * a fixed array inside the library instead. The caller passes only inputs
+ * (q, k, v, out, dout, lse) and outputs (dq, dk, dv: element type `dtype`,
+ * contiguous [B,Sq,Hq,D] / [B,Sk,Hkv,D], overwritten).
+ *
+ * - It calls no cudaMalloc/cudaFree and no allocating library routine.
+ * - Limit: B*Sq*Hq*(D+1)*4 bytes (rounded up to 256) must fit in
+ *   SPA_NOALLOC_SCRATCH_BYTES; larger problems are rejected with SPA_EINVAL.
+ *   Every GPU that loads the library holds that array until the process exits.
+ * - The first call on a device looks up the array's device address; make that
+ *   first call before starting any stream capture.
+ * - All calls share the one array (it is re-zeroed at the start of each call):
+ *   calls that overlap on the same GPU, e.g. from two streams, race. Serialise them.
+ * - The arithmetic runs on the fp32 CUDA-core kernels for every dtype.
+ */
+#define SPA_NOALLOC_SCRATCH_BYTES (64u << 20)
+
+typedef struct spa_bwd_noalloc_args {
+  const void* q;    int64_t q_sb, q_ss, q_sh;
+  const void* k;    int64_t k_sb, k_ss, k_sh;
+  const void* v;    int64_t v_sb, v_ss, v_sh;
+  const void* out;  int64_t o_sb, o_ss, o_sh;
+  const void* dout; int64_t do_sb, do_ss, do_sh;
+  const float* lse;      /* [B,Hq,Sq] */
+  void* dq;              /* [B,Sq,Hq,D] contiguous */
+  void* dk;              /* [B,Sk,Hkv,D] contiguous */
+  void* dv;
+  int32_t B, Sq, Sk, Hq, Hkv, D;
+  int32_t dtype;
+  int32_t causal;
+  int32_t causal_off;
+  float scale;
+  void* stream;
+} spa_bwd_noalloc_args;
+
+int spa_attn_bwd_noalloc(const spa_bwd_noalloc_args* args);
+
+/* Size of the built-in scratch array, in bytes. */
+int64_t spa_noalloc_scratch_bytes(void);
+
+/*
  * Stand-alone out/lse merge (the fused epilogue of spa_attn_fwd does the same
  * arithmetic; this entry exists for callers that hold two partial results).
  * Replaces: sp_aurora/utils.py:109 update_out_and_lse / :47 _update_out_and_lse.

@@ -54,11 +54,30 @@ class BwdArgs(C.Structure):
     ]
 
 
+class BwdNoallocArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("q_sb", C.c_int64), ("q_ss", C.c_int64), ("q_sh", C.c_int64),
+        ("k", C.c_void_p), ("k_sb", C.c_int64), ("k_ss", C.c_int64), ("k_sh", C.c_int64),
+        ("v", C.c_void_p), ("v_sb", C.c_int64), ("v_ss", C.c_int64), ("v_sh", C.c_int64),
+        ("out", C.c_void_p), ("o_sb", C.c_int64), ("o_ss", C.c_int64), ("o_sh", C.c_int64),
+        ("dout", C.c_void_p), ("do_sb", C.c_int64), ("do_ss", C.c_int64), ("do_sh", C.c_int64),
+        ("lse", C.c_void_p),
+        ("dq", C.c_void_p), ("dk", C.c_void_p), ("dv", C.c_void_p),
+        ("B", C.c_int32), ("Sq", C.c_int32), ("Sk", C.c_int32),
+        ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32),
+        ("dtype", C.c_int32), ("causal", C.c_int32), ("causal_off", C.c_int32),
+        ("scale", C.c_float),
+        ("stream", C.c_void_p),
+    ]
+
+
 # Every symbol include/spa.h declares, with its ctypes signature.
 _I64x4 = C.c_int64 * 4
 _SIGNATURES = {
     "spa_attn_fwd": (C.c_int, [C.POINTER(FwdArgs)]),
     "spa_attn_bwd": (C.c_int, [C.POINTER(BwdArgs)]),
+    "spa_attn_bwd_noalloc": (C.c_int, [C.POINTER(BwdNoallocArgs)]),
+    "spa_noalloc_scratch_bytes": (C.c_int64, []),
     "spa_bwd_delta": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                 C.c_void_p, C.c_int64, C.c_int64, C.c_int64,
                                 C.c_void_p, C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
@@ -79,7 +98,21 @@ _SIGNATURES = {
 }
 
 
+def _rebuild_if_stale() -> None:
+    """Developer convenience: when a compiler is present and a source file is
+    newer than the library, recompile before loading (never a fallback: without
+    nvcc a stale or missing library still fails below)."""
+    from . import build as _build   # plain build recipe, does not load the library
+    try:
+        stale = _build._stale(_LIB_PATH, [_build.CSRC / s for s in _build.SOURCES] + _build.HEADERS)
+        if stale:
+            _build.build()
+    except RuntimeError:
+        pass
+
+
 def _load() -> C.CDLL:
+    _rebuild_if_stale()
     if not _LIB_PATH.exists():
         raise ImportError(
             f"{_LIB_PATH} is missing: build it with `python -m sp_aurora_b200.build` "

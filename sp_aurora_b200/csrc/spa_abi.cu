@@ -509,4 +509,96 @@ int spa_permute_rows(const void* src, void* dst, const int64_t n[4], const int64
   return rc;
 }
 
+
+// ---------------------------------------------------------------------------
+// Allocation-free backward.
+//
+// Some callers may not allocate device memory at all: code running inside a
+// memory pool that already owns the whole GPU, a service with a fixed memory
+// budget, or a host thread that must not take the allocator's locks. For them
+// the scratch of the backward pass (the fp32 dq accumulator and the delta row
+// sums) lives in the fixed array below instead of in caller-provided buffers.
+// The array is part of the library image: every GPU that loads the library
+// holds SPA_NOALLOC_SCRATCH_BYTES of it until the process exits.
+// ---------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_noalloc_scratch[SPA_NOALLOC_SCRATCH_BYTES];
+
+// In host code `g_noalloc_scratch` is only a handle; the device address has to
+// be asked for, once per device, with that device current.
+static std::mutex g_noalloc_mu;
+static unsigned char* g_noalloc_ptr[64] = {nullptr};
+
+static unsigned char* noalloc_scratch_ptr() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("cudaGetDevice failed");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+    if (e != cudaSuccess || !ptr) {
+      set_error("cudaGetSymbolAddress(scratch): %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    g_noalloc_ptr[dev] = static_cast<unsigned char*>(ptr);
+  }
+  return g_noalloc_ptr[dev];
+}
+
+int64_t spa_noalloc_scratch_bytes(void) { return (int64_t)SPA_NOALLOC_SCRATCH_BYTES; }
+
+int spa_attn_bwd_noalloc(const spa_bwd_noalloc_args* a) {
+  if (!a || !a->q || !a->k || !a->v || !a->out || !a->dout || !a->lse || !a->dq || !a->dk ||
+      !a->dv) {
+    set_error("spa_attn_bwd_noalloc: null pointer argument");
+    return SPA_EINVAL;
+  }
+  int rc = validate_common(a->B, a->Sq, a->Sk, a->Hq, a->Hkv, a->D, a->dtype, a->scale);
+  if (rc) return rc;
+  const size_t rows = (size_t)a->B * a->Sq * a->Hq;
+  const size_t delta_bytes = (rows * sizeof(float) + 255) & ~(size_t)255;
+  const size_t dq_bytes = rows * a->D * sizeof(float);
+  if (delta_bytes + dq_bytes > (size_t)SPA_NOALLOC_SCRATCH_BYTES) {
+    set_error("spa_attn_bwd_noalloc: B*Sq*Hq*(D+1)*4 = %zu bytes of scratch needed, the built-in "
+              "scratch holds %zu; use spa_attn_bwd with caller-provided buffers",
+              delta_bytes + dq_bytes, (size_t)SPA_NOALLOC_SCRATCH_BYTES);
+    return SPA_EINVAL;
+  }
+  unsigned char* base = noalloc_scratch_ptr();
+  if (!base) return SPA_ECUDA;
+  float* delta = reinterpret_cast<float*>(base);
+  float* dq_acc = reinterpret_cast<float*>(base + delta_bytes);
+  cudaStream_t st = (cudaStream_t)a->stream;
+  // The array keeps whatever the last call left: the accumulator starts at zero.
+  cudaError_t e = cudaMemsetAsync(dq_acc, 0, dq_bytes, st);
+  if (e != cudaSuccess) {
+    set_error("spa_attn_bwd_noalloc: memset: %s", cudaGetErrorString(e));
+    return SPA_ECUDA;
+  }
+  rc = spa_bwd_delta(a->out, a->o_sb, a->o_ss, a->o_sh, a->dout, a->do_sb, a->do_ss, a->do_sh, delta,
+                     a->B, a->Sq, a->Hq, a->D, a->dtype, a->stream);
+  if (rc) return rc;
+  spa_bwd_args b;
+  memset(&b, 0, sizeof(b));
+  b.q = a->q; b.q_sb = a->q_sb; b.q_ss = a->q_ss; b.q_sh = a->q_sh;
+  b.k = a->k; b.k_sb = a->k_sb; b.k_ss = a->k_ss; b.k_sh = a->k_sh;
+  b.v = a->v; b.v_sb = a->v_sb; b.v_ss = a->v_ss; b.v_sh = a->v_sh;
+  b.dout = a->dout; b.do_sb = a->do_sb; b.do_ss = a->do_ss; b.do_sh = a->do_sh;
+  b.lse = a->lse; b.delta = delta; b.dq_acc = dq_acc; b.dk = a->dk; b.dv = a->dv;
+  b.dkv_fp32 = 0; b.dkv_accumulate = 0;
+  b.B = a->B; b.Sq = a->Sq; b.Sk = a->Sk; b.Hq = a->Hq; b.Hkv = a->Hkv; b.D = a->D;
+  b.dtype = a->dtype; b.causal = a->causal; b.causal_off = a->causal_off; b.scale = a->scale;
+  b.stream = a->stream;
+  // CUDA-core kernels: they need neither the status word nor any other
+  // allocation; dq rows are owned by one CTA each, dk/dv are written directly.
+  rc = launch_bwd_simt(&b);
+  if (rc) return rc;
+  note_launch(2);
+  const int64_t d_ss = (int64_t)a->Hq * a->D, d_sb = (int64_t)a->Sq * d_ss;
+  return spa_cast_from_f32(dq_acc, a->dq, d_sb, d_ss, a->D, a->B, a->Sq, a->Hq, a->D, a->dtype, 1.0f,
+                           a->stream);
+}
+
 }  // extern "C"
