@@ -23,7 +23,9 @@ from typing import Callable, List, Optional, Tuple
 import torch
 import torch.distributed as dist
 
-from . import local_attn
+import os
+
+from . import local_attn, zigzag
 from .local_attn import check_unsupported_kwargs
 
 __all__ = [
@@ -205,6 +207,16 @@ def ring_flash_attn_backward(process_group, dout, q, k, v, out, softmax_lse, sof
     return cast_fn(dq_acc, q.dtype), cast_fn(next_dkv[0], q.dtype), cast_fn(next_dkv[1], q.dtype)
 
 
+def _use_zigzag(group, q, causal) -> bool:
+    """Causal rings of more than one rank run on the internally re-balanced
+    (zigzag) layout; SPA_RING_ZIGZAG=0 keeps the plain contiguous schedule."""
+    if not causal or not (dist.is_available() and dist.is_initialized()):
+        return False
+    if dist.get_world_size(group) == 1 or q.shape[1] % 2:
+        return False
+    return os.environ.get("SPA_RING_ZIGZAG", "1") != "0"
+
+
 class RingFlashAttnFunc(torch.autograd.Function):
     """Counterpart of sp_aurora/intel_ring_flash_attn.py:274 IntelRingFlashAttnFunc."""
 
@@ -215,8 +227,13 @@ class RingFlashAttnFunc(torch.autograd.Function):
         if softmax_scale is None:
             softmax_scale = q.shape[-1] ** (-0.5)
         local_attn.check_qkv(q, k, v)
-        out, lse = ring_flash_attn_forward(group, q, k, v, softmax_scale, causal)
-        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.zigzag = _use_zigzag(group, q, causal)
+        if ctx.zigzag:
+            out, lse, saved = zigzag.zigzag_ring_forward(group, q, k, v, softmax_scale)
+            ctx.save_for_backward(*saved)
+        else:
+            out, lse = ring_flash_attn_forward(group, q, k, v, softmax_scale, causal)
+            ctx.save_for_backward(q, k, v, out, lse)
         ctx.softmax_scale = softmax_scale
         ctx.causal = causal
         ctx.group = group
@@ -224,9 +241,14 @@ class RingFlashAttnFunc(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, dout, *args):
-        q, k, v, out, lse = ctx.saved_tensors
         if dout.stride(-1) != 1:
             dout = dout.contiguous()
+        if ctx.zigzag:
+            q_z, kv_z, out_z, lse_z = ctx.saved_tensors
+            dq, dk, dv = zigzag.zigzag_ring_backward(ctx.group, dout, q_z, kv_z, out_z, lse_z,
+                                                     ctx.softmax_scale)
+            return dq, dk, dv, None, None, None, None, None, None, None, None
+        q, k, v, out, lse = ctx.saved_tensors
         dq, dk, dv = ring_flash_attn_backward(ctx.group, dout, q, k, v, out, lse,
                                               ctx.softmax_scale, ctx.causal)
         return dq, dk, dv, None, None, None, None, None, None, None, None

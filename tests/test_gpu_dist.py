@@ -44,10 +44,14 @@ def _worker(rank, world, port, ret):
         sl_of = lambda S: slice(rank * (S // world), (rank + 1) * (S // world))
 
         # ---- ring: fp32 anchor (B2 S1024 H32 D64 causal at W=2) and bf16 GQA kv-packed
+        # causal rings run on the balanced (zigzag) schedule by default; "_contig"
+        # repeats one case on the plain contiguous-shard schedule
         for tag, dtype, B, S, Hq, Hkv, D, causal, tol in (
                 ("ring_fp32", torch.float32, 2, 1024, 32, 32, 64, True, 1e-4),
                 ("ring_bf16_gqa", torch.bfloat16, 1, 2048, 8, 2, 128, True, 2e-2),
+                ("ring_bf16_gqa_contig", torch.bfloat16, 1, 2048, 8, 2, 128, True, 2e-2),
                 ("ring_bf16_noncausal", torch.bfloat16, 1, 1024, 4, 4, 128, False, 2e-2)):
+            os.environ["SPA_RING_ZIGZAG"] = "0" if tag.endswith("_contig") else "1"
             q = _rand((B, S, Hq, D), 1).to(dtype)
             kv = _rand((B, S, 2, Hkv, D), 2).to(dtype)
             do = _rand((B, S, Hq, D), 3).to(dtype)
@@ -130,7 +134,7 @@ def results():
     return out
 
 
-@pytest.mark.parametrize("tag", ["ring_fp32", "ring_bf16_gqa", "ring_bf16_noncausal", "uly_b2",
+@pytest.mark.parametrize("tag", ["ring_fp32", "ring_bf16_gqa", "ring_bf16_gqa_contig", "ring_bf16_noncausal", "uly_b2",
                                  "uly_gqa_causal", "a2a_exact", "hyb_u", "hyb_r"])
 def test_multi_gpu_parity(results, tag):
     for r, res in results.items():

@@ -113,6 +113,54 @@ def _host_copy(dst, src):
     return dst
 
 
+def _zigzag_errs(rank, world, orc):
+    """Balanced causal ring (internal zigzag re-layout) vs the full-sequence oracle."""
+    from sp_aurora_b200 import zigzag
+    errs = {}
+    for hq, hkv in ((4, 4), (4, 2)):
+        g = torch.Generator().manual_seed(21)
+        B, S, D = 2, 32 * world, 16
+        q = torch.randn(B, S, hq, D, generator=g)
+        k = torch.randn(B, S, hkv, D, generator=g)
+        v = torch.randn(B, S, hkv, D, generator=g)
+        dout = torch.randn(B, S, hq, D, generator=g)
+        full_out, full_lse = orc.attention_ref(q, k, v, None, True)
+        fdq, fdk, fdv = orc.attention_bwd_ref(dout, q, k, v, full_out, full_lse, None, True)
+        sl = S // world
+        sli = slice(rank * sl, (rank + 1) * sl)
+        qs, ks, vs, ds = (t[:, sli].contiguous() for t in (q, k, v, dout))
+        out, lse, saved = zigzag.zigzag_ring_forward(None, qs, ks, vs, D ** -0.5,
+                                                     fwd_step=orc.fwd_step_cpu, cast_fn=orc.cast_cpu)
+        dq, dk, dv = zigzag.zigzag_ring_backward(None, ds, *saved, D ** -0.5,
+                                                 bwd_step=orc.bwd_step_cpu, delta_fn=orc.delta_cpu,
+                                                 cast_fn=orc.cast_cpu)
+        errs[(hq, hkv)] = [
+            float((out.double() - full_out[:, sli]).abs().max()),
+            float((lse.double() - full_lse[:, :, sli]).abs().max()),
+            float((dq.double() - fdq[:, sli]).abs().max()),
+            float((dk.double() - fdk[:, sli]).abs().max()),
+            float((dv.double() - fdv[:, sli]).abs().max())]
+    return errs
+
+
+def _worker4(rank, world, port, ret):
+    import sys
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    torch.set_num_threads(1)
+    from oracle import attention_oracle as orc
+    res = {}
+    try:
+        res["zigzag_errs"] = _zigzag_errs(rank, world, orc)
+    except Exception:  # noqa: BLE001
+        import traceback
+        res["error"] = traceback.format_exc()
+    ret[rank] = res
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def _worker(rank, world, port, golden, ret):
     import sys
     sys.path.insert(0, ROOT)
@@ -177,6 +225,7 @@ def _worker(rank, world, port, golden, ret):
                 float((dk.double() - fdk[:, sli]).abs().max()),
                 float((dv.double() - fdv[:, sli]).abs().max())]
         res["ring_errs"] = errs
+        res["zigzag_errs"] = _zigzag_errs(rank, world, orc)
     except Exception as e:  # noqa: BLE001
         import traceback
         res["error"] = traceback.format_exc()
@@ -210,3 +259,30 @@ def test_gloo_ring_schedule_forward_backward(gloo_results):
     for r in range(2):
         for key, errs in gloo_results[r]["ring_errs"].items():
             assert max(errs) < 2e-5, (r, key, errs)   # fp32 hand-off between steps
+
+
+def test_gloo_zigzag_ring_two_ranks(gloo_results):
+    for r in range(2):
+        for key, errs in gloo_results[r]["zigzag_errs"].items():
+            assert max(errs) < 2e-5, (r, key, errs)
+
+
+def test_gloo_zigzag_ring_four_ranks():
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_worker4, args=(4, _free_port(), ret), nprocs=4, join=True)
+    for r in range(4):
+        res = dict(ret[r])
+        assert "error" not in res, res.get("error")
+        for key, errs in res["zigzag_errs"].items():
+            assert max(errs) < 2e-5, (r, key, errs)
+
+
+def test_zigzag_plan_is_balanced():
+    from sp_aurora_b200.zigzag import _step_calls, half_owner
+    for W in (2, 4, 8):
+        owners = sorted(half_owner(c, W) for c in range(2 * W))
+        assert owners == sorted((r, s) for r in range(W) for s in (0, 1))
+        for r in range(W):
+            work = [sum(0.5 if c[2] else 1.0 for c in _step_calls(s, r, W)) for s in range(W)]
+            assert work == [2.0] * W          # every rank, every step: two half-blocks
