@@ -243,7 +243,7 @@ def main():
     timers = local_attn.KERNEL_TIMERS
     local_attn.KERNEL_TIMERS = None
     clocks = sampler.stop() if rank == 0 else None
-    kt = {k: [a.elapsed_time(b) for a, b in v] for k, v in timers.items()}
+    kt = {k: [(a.elapsed_time(b_), f) for a, b_, f in v] for k, v in timers.items()}
     t = torch.tensor([ms], device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -285,18 +285,16 @@ def main():
     peak_burst = peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])
 
     if rank == 0:
-        # dominant kernel = backward; algorithmic FLOPs per launch = 2.5x forward of
-        # the blocks this rank computes per step, averaged over its launches
-        bwd_ms = kt.get("bwd", [])
-        fwd_ms = kt.get("fwd", [])
-        n_b = max(1, len(bwd_ms))
-        # rank 0 of a causal ring computes only its diagonal block each step
-        sl = args.seq // world
-        rank0_fwd = 4.0 * B * HQ * sl * sl * D / 2
-        bwd_flops_per_launch = 2.5 * rank0_fwd
-        avg_bwd = sum(bwd_ms) / n_b if bwd_ms else float("nan")
-        achieved = bwd_flops_per_launch / (avg_bwd * 1e-3) / 1e12 if bwd_ms else None
-        avg_fwd = sum(fwd_ms) / max(1, len(fwd_ms)) if fwd_ms else float("nan")
+        # dominant kernel = backward; achieved = algorithmic FLOPs of this rank's
+        # launches / their summed CUDA-event durations inside the timed region
+        def rate(name):
+            rows = kt.get(name, [])
+            t_ms = sum(t for t, _ in rows)
+            fl = sum(f for _, f in rows)
+            n = max(1, len(rows))
+            return (fl / (t_ms * 1e-3) / 1e12 if t_ms > 0 else None), (t_ms / n if rows else None), len(rows), fl / n
+        achieved, avg_bwd, n_bwd, bwd_flops_per_launch = rate("bwd")
+        fwd_rate, avg_fwd, n_fwd, _ = rate("fwd")
         line = {
             "metric": "ring_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -310,9 +308,10 @@ def main():
                          "achieved": achieved, "peak": peak_sust, "unit": "TFLOP/s",
                          "frac": (achieved / peak_sust) if achieved else None,
                          "peak_source": f"{peak_kind} bf16_tflops_sustained", "traffic": None,
-                         "avg_launch_ms": avg_bwd, "launches_timed": len(bwd_ms),
-                         "fwd_kernel": {"avg_launch_ms": avg_fwd,
-                                        "achieved": (rank0_fwd / (avg_fwd * 1e-3) / 1e12) if fwd_ms else None}},
+                         "avg_launch_ms": avg_bwd, "launches_timed": n_bwd,
+                         "flops_per_launch": bwd_flops_per_launch,
+                         "fwd_kernel": {"avg_launch_ms": avg_fwd, "launches_timed": n_fwd,
+                                        "achieved": fwd_rate}},
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                     "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": int(world * (hq.numel() + hkv.numel() + hdo.numel()) * 2),

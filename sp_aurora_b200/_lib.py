@@ -10,7 +10,11 @@ from pathlib import Path
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent / "libspaurora_sm100.so"
+import os
+
+# SPA_LIB_PATH lets a developer load another build of the same library (A/B timing).
+_LIB_PATH = Path(os.environ.get("SPA_LIB_PATH") or
+                 Path(__file__).resolve().parent / "libspaurora_sm100.so")
 
 SPA_OK = 0
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
@@ -103,6 +107,8 @@ def _rebuild_if_stale() -> None:
     newer than the library, recompile before loading (never a fallback: without
     nvcc a stale or missing library still fails below)."""
     from . import build as _build   # plain build recipe, does not load the library
+    if os.environ.get("SPA_LIB_PATH"):
+        return
     try:
         stale = _build._stale(_LIB_PATH, [_build.CSRC / s for s in _build.SOURCES] + _build.HEADERS)
         if stale:

@@ -24,10 +24,15 @@
 //   warps 8-11  dQ drain group: head-dim lane per thread; TMEM -> shared memory
 //               (fp32 [64 queries][D]) -> one TMA reduce-add into the dq accumulator
 //   warp  12    TMA producer          warp 13  MMA issuer and TMEM owner
-// TMEM columns: S^T [0,64) dP^T [64,128) dV [128,128+D) dK [256,256+D) dQ^T [384,448).
+// TMEM columns: S^T [0,64) dP^T [64,128) dV [128,128+D) dK [256,256+D) dQ^T [384,448)
+// P^T [448,480) dS^T [480,512) (16-bit, two per column): the A operands of the dV and
+// dK products are read from TMEM, so P never touches shared memory and dS is
+// written there only once (as the B operand of dQ^T). Shared-memory bandwidth
+// (128 B/clk) is what bounds this kernel.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include <type_traits>
 
@@ -37,6 +42,18 @@
 namespace spa {
 namespace {
 
+// Debug timeline (compile with -DSPA_TRACE, run with SPA_WAIT_PROFILE=1): block 0
+// records clock64 at event `ev` of iterations [64, 72) into p.prof[ev * 8 + it - 64].
+#ifdef SPA_TRACE
+#define SPA_TRACE_EV(ev, it)                                                              \
+  do {                                                                                    \
+    if (p.prof && blockIdx.x == 0 && (it) >= 64 && (it) < 72 && (threadIdx.x & 31) == 0)  \
+      p.prof[32 + (ev) * 8 + (it) - 64] = (unsigned long long)clock64();                  \
+  } while (0)
+#else
+#define SPA_TRACE_EV(ev, it) do { } while (0)
+#endif
+
 constexpr int kTileKV = 128;
 constexpr int kTileQ = 64;
 constexpr int kThreads = 448;
@@ -45,11 +62,14 @@ constexpr int kStages = 3;
 constexpr float kLog2e = 1.4426950408889634f;
 
 constexpr uint32_t kColS = 0, kColDP = 64, kColDV = 128, kColDK = 256, kColDQ = 384;
+constexpr uint32_t kColP = 448, kColDS = 480;
 
 struct BwdParams {
   int B, Sq, Sk, Hq, Hkv;
   int causal, causal_off;
   int dkv_fp32, dkv_accumulate;
+  int drain_red;   // 1: dQ leaves by per-thread red.global.add, 0: shared staging + TMA reduce
+  int tmem_ops;    // 1: P^T / dS^T feed dV / dK from TMEM, 0: from shared memory
   int n_kvblk;
   float scale, scale_log2;
   const float* lse;
@@ -58,6 +78,7 @@ struct BwdParams {
   void* dk;
   void* dv;
   int* status;
+  unsigned long long* prof;  // optional global array [32] of blocked cycles per wait site
 };
 
 template <int D>
@@ -77,7 +98,8 @@ struct BwdSmem {
   static constexpr int kRowOff = kDQOff + kTileQ * D * 4;    // lse2/delta [2][2][64] floats
   static constexpr int kBarOff = kRowOff + 2 * 2 * 64 * 4;
   static constexpr int kNumBars = 1 + 2 * kStages + 8;
-  static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
+  static constexpr int kProfOff = kBarOff + kNumBars * 8 + 16;   // 32 x u64 wait profile
+  static constexpr int kTotal = kProfOff + 32 * 8;
 };
 
 template <typename T>
@@ -145,6 +167,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int n_q = i_end - i_start;
   const int n_it = n_q * G;
 
+  if (threadIdx.x < 32) reinterpret_cast<unsigned long long*>(smem + L::kProfOff)[threadIdx.x] = 0;
   if (threadIdx.x == 0) {
     *cta_abort = 0;
     mbar_init(kv_full, 1);
@@ -171,7 +194,9 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  WaitCtx wc{p.status, cta_abort};
+  unsigned long long* prof_s = reinterpret_cast<unsigned long long*>(smem + L::kProfOff);
+  WaitCtx wc{p.status, cta_abort, p.prof ? prof_s : nullptr};
+  const long long t_start = clock64();
 
   if (warp == kWarpTma) {
     // ------------------------------------------------------------------ TMA
@@ -188,7 +213,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       for (int it = 0; it < n_it; ++it) {
         const int slot = it % kStages;
         const uint32_t ph = (it / kStages) & 1;
-        if (!mbar_wait(&qdo_empty[slot], ph ^ 1, wc, 100, it)) break;
+        if (!mbar_wait(&qdo_empty[slot], ph ^ 1, wc, 0, it)) break;
         const int hq = g * G + it / n_q;
         const int q0 = (i_start + it % n_q) * kTileQ;
         uint8_t* st = smem + L::kStageOff + slot * L::kStageBytes;
@@ -201,7 +226,10 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA
-    if (lane == 0 && n_it > 0) {
+    // Every lane runs this code with identical values; only the tcgen05
+    // instructions are predicated on the leader lane.
+    if (n_it > 0) {
+      const uint32_t leader = lane == 0;
       constexpr uint32_t idesc_sdp = make_idesc(128, kTileQ, kBf16, false, false);
       constexpr uint32_t idesc_dkv = make_idesc(128, D, kBf16, false, true);
       constexpr uint32_t idesc_dq = make_idesc(128, kTileQ, kBf16, true, true);
@@ -211,70 +239,91 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       const uint32_t st_base = smem_u32(smem + L::kStageOff);
       const uint32_t p_base = smem_u32(smem + L::kPOff);
       const uint32_t ds_base = smem_u32(smem + L::kDSOff);
-      bool ok = mbar_wait(kv_full, 0, wc, 200, 0);
+      bool ok = mbar_wait(kv_full, 0, wc, 1, 0);
       tc_fence_after();
 
+      const SmemDesc k_km = make_smem_desc(k_base, 16, 1024);        // K tile, K-major (S^T)
+      const SmemDesc v_km = make_smem_desc(v_base, 16, 1024);        // V tile, K-major (dP^T)
+      const SmemDesc k_mn = make_smem_desc(k_base, kLboK, 1024);     // K tile, MN-major (dQ^T)
+      const SmemDesc st_km = make_smem_desc(st_base, 16, 1024);      // Q / dO stage, K-major
+      const SmemDesc st_mn = make_smem_desc(st_base, L::kQSlab, 1024);  // Q / dO stage, MN-major
+      const SmemDesc p_km = make_smem_desc(p_base, 16, 1024);        // P^T (shared-memory variant)
+      const SmemDesc ds_km = make_smem_desc(ds_base, 16, 1024);      // dS^T as A of dK
+      const SmemDesc ds_mn = make_smem_desc(ds_base, 16, 1024);      // dS^T as B of dQ^T
       auto issue_sdp = [&](int it) -> bool {
         const int slot = it % kStages;
-        if (!mbar_wait(&qdo_full[slot], (it / kStages) & 1, wc, 201, it)) return false;
+        if (!mbar_wait(&qdo_full[slot], (it / kStages) & 1, wc, 2, it)) return false;
         tc_fence_after();
-        const uint32_t qb = st_base + slot * L::kStageBytes;
-        const uint32_t dob = qb + L::kQTile;
+        const uint32_t qb = (slot * L::kStageBytes) >> 4;
+        const uint32_t dob = qb + (L::kQTile >> 4);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t aoff = (kk / 4) * L::kKVSlab + (kk % 4) * 32;
-          const uint32_t boff = (kk / 4) * L::kQSlab + (kk % 4) * 32;
-          mma_ss(tmem_base + kColS, smem_desc_sw128(k_base + aoff, 16, 1024),
-                 smem_desc_sw128(qb + boff, 16, 1024), idesc_sdp, kk > 0);
+          const uint32_t aoff = ((kk / 4) * L::kKVSlab + (kk % 4) * 32) >> 4;
+          const uint32_t boff = ((kk / 4) * L::kQSlab + (kk % 4) * 32) >> 4;
+          mma_ss_u(tmem_base + kColS, k_km, aoff, st_km, qb + boff, idesc_sdp, kk > 0, leader);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t aoff = (kk / 4) * L::kKVSlab + (kk % 4) * 32;
-          const uint32_t boff = (kk / 4) * L::kQSlab + (kk % 4) * 32;
-          mma_ss(tmem_base + kColDP, smem_desc_sw128(v_base + aoff, 16, 1024),
-                 smem_desc_sw128(dob + boff, 16, 1024), idesc_sdp, kk > 0);
+          const uint32_t aoff = ((kk / 4) * L::kKVSlab + (kk % 4) * 32) >> 4;
+          const uint32_t boff = ((kk / 4) * L::kQSlab + (kk % 4) * 32) >> 4;
+          mma_ss_u(tmem_base + kColDP, v_km, aoff, st_km, dob + boff, idesc_sdp, kk > 0, leader);
         }
-        mma_commit(sdp_full);
+        mma_commit_u(sdp_full, leader);
+        SPA_TRACE_EV(0, it);
         return true;
       };
 
       if (ok) ok = issue_sdp(0);
       for (int it = 0; it < n_it && ok; ++it) {
         if (it + 1 < n_it) {
-          ok = mbar_wait(sdp_free, it & 1, wc, 202, it);
+          ok = mbar_wait(sdp_free, it & 1, wc, 3, it);
           if (!ok) break;
           tc_fence_after();
           ok = issue_sdp(it + 1);
           if (!ok) break;
         }
-        ok = mbar_wait(pds_full, it & 1, wc, 203, it);
+        ok = mbar_wait(pds_full, it & 1, wc, 4, it);
         if (!ok) break;
         tc_fence_after();
+        SPA_TRACE_EV(1, it);
         const int slot = it % kStages;
-        const uint32_t qb = st_base + slot * L::kStageBytes;
-        const uint32_t dob = qb + L::kQTile;
-        // dV += P^T dO ; dK += dS^T Q   (A K-major over queries, B MN-major)
+        const uint32_t qb = (slot * L::kStageBytes) >> 4;
+        const uint32_t dob = qb + (L::kQTile >> 4);
+        // dV += P^T dO ; dK += dS^T Q : B = dO / Q stage read MN-major; A = P^T / dS^T
+        // from TMEM (tmem_ops) or from shared memory.
+        if (p.tmem_ops) {
 #pragma unroll
-        for (int kk = 0; kk < kTileQ / 16; ++kk)
-          mma_ss(tmem_base + kColDV, smem_desc_sw128(p_base + kk * 32, 16, 1024),
-                 smem_desc_sw128(dob + kk * 2048, L::kQSlab, 1024), idesc_dkv, (it > 0 || kk > 0));
+          for (int kk = 0; kk < kTileQ / 16; ++kk)
+            mma_ts_u(tmem_base + kColDV, tmem_base + kColP + kk * 8, st_mn, dob + ((kk * 2048) >> 4),
+                     idesc_dkv, (it > 0 || kk > 0), leader);
 #pragma unroll
-        for (int kk = 0; kk < kTileQ / 16; ++kk)
-          mma_ss(tmem_base + kColDK, smem_desc_sw128(ds_base + kk * 32, 16, 1024),
-                 smem_desc_sw128(qb + kk * 2048, L::kQSlab, 1024), idesc_dkv, (it > 0 || kk > 0));
+          for (int kk = 0; kk < kTileQ / 16; ++kk)
+            mma_ts_u(tmem_base + kColDK, tmem_base + kColDS + kk * 8, st_mn, qb + ((kk * 2048) >> 4),
+                     idesc_dkv, (it > 0 || kk > 0), leader);
+        } else {
+#pragma unroll
+          for (int kk = 0; kk < kTileQ / 16; ++kk)
+            mma_ss_u(tmem_base + kColDV, p_km, (kk * 32) >> 4, st_mn, dob + ((kk * 2048) >> 4),
+                     idesc_dkv, (it > 0 || kk > 0), leader);
+#pragma unroll
+          for (int kk = 0; kk < kTileQ / 16; ++kk)
+            mma_ss_u(tmem_base + kColDK, ds_km, (kk * 32) >> 4, st_mn, qb + ((kk * 2048) >> 4),
+                     idesc_dkv, (it > 0 || kk > 0), leader);
+        }
         // dQ^T = K^T dS : A = K tile read MN-major (M = head dim), B = dS^T tile
         // read MN-major (N = queries), contraction over the 128 keys.
         if (it > 0) {
-          ok = mbar_wait(dq_free, (it - 1) & 1, wc, 204, it);
+          ok = mbar_wait(dq_free, (it - 1) & 1, wc, 5, it);
           if (!ok) break;
           tc_fence_after();
         }
 #pragma unroll
         for (int kk = 0; kk < kTileKV / 16; ++kk)
-          mma_ss(tmem_base + kColDQ, smem_desc_sw128(k_base + kk * 2048, kLboK, 1024),
-                 smem_desc_sw128(ds_base + kk * 2048, 16, 1024), idesc_dq, kk > 0);
-        mma_commit(mma_done);
-        mma_commit(&qdo_empty[slot]);
+          mma_ss_u(tmem_base + kColDQ, k_mn, (kk * 2048) >> 4, ds_mn, (kk * 2048) >> 4, idesc_dq,
+                   kk > 0, leader);
+        mma_commit_u(mma_done, leader);
+        SPA_TRACE_EV(2, it);
+        mma_commit_u(&qdo_empty[slot], leader);
       }
     }
   } else if (warp >= 8) {
@@ -288,17 +337,37 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     float* stage = reinterpret_cast<float*>(smem + L::kDQOff);
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
-      ok = warp_wait(mma_done, it & 1, wc, 400, it);
+      ok = warp_wait(mma_done, it & 1, wc, 16, it);
       if (!ok) break;
       tc_fence_after();
+      if (warp == 8) SPA_TRACE_EV(8, it);
       uint32_t v0[32], v1[32];
       tmem_ld32(t_dq, v0);
       tmem_ld32(t_dq + 32, v1);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(dq_free);
+      if (warp == 8) SPA_TRACE_EV(9, it);
+      if (p.drain_red) {
+        // straight from registers: lane = head-dim index, one coalesced 128-byte
+        // reduction per query row and warp
+        if (d < D) {
+          const int hq = g * G + it / n_q;
+          const int q0 = (i_start + it % n_q) * kTileQ;
+          float* base = p.dq_acc + (((size_t)b * p.Sq + q0) * p.Hq + hq) * D + d;
+          const size_t rs = (size_t)p.Hq * D;
+          const int nvalid = p.Sq - q0;
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (i < nvalid) atomicAdd(base + i * rs, __uint_as_float(v0[i]) * p.scale);
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (32 + i < nvalid) atomicAdd(base + (32 + i) * rs, __uint_as_float(v1[i]) * p.scale);
+        }
+        continue;
+      }
       // staging buffer must have been read by the previous reduce
-      ok = warp_wait(stage_free, (it & 1) ^ 1, wc, 401, it);
+      ok = warp_wait(stage_free, (it & 1) ^ 1, wc, 17, it);
       if (!ok) break;
       if (d < D) {
 #pragma unroll
@@ -309,8 +378,9 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       fence_proxy_async_smem();
       mbar_arrive(stage_full);
+      if (warp == 8) SPA_TRACE_EV(10, it);
       if (tid == 0) {
-        ok = mbar_wait(stage_full, it & 1, wc, 402, it);
+        ok = mbar_wait(stage_full, it & 1, wc, 18, it);
         if (ok) {
           const int hq = g * G + it / n_q;
           const int q0 = (i_start + it % n_q) * kTileQ;
@@ -336,6 +406,8 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t t_dp = tmem_base + lane_field + kColDP + c_base;
     const uint32_t t_dv = tmem_base + lane_field + kColDV;
     const uint32_t t_dk = tmem_base + lane_field + kColDK;
+    const uint32_t t_p = tmem_base + lane_field + kColP + grp * 16;
+    const uint32_t t_ds = tmem_base + lane_field + kColDS + grp * 16;
     uint8_t* p_row = smem + L::kPOff;
     uint8_t* ds_row = smem + L::kDSOff;
     const bool key_ok = kidx < p.Sk;
@@ -363,19 +435,21 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       float next_stat = 0.f;
       if (grp == 0 && it + 1 < n_it) next_stat = fetch_rowstat(it + 1);
 
-      ok = warp_wait(sdp_full, it & 1, wc, 300, it);
+      ok = warp_wait(sdp_full, it & 1, wc, 8, it);
       if (!ok) break;
       tc_fence_after();
+      if (warp == 0) SPA_TRACE_EV(3, it);
       uint32_t sr[32], dpr[32];
       tmem_ld32(t_s, sr);
       tmem_ld32(t_dp, dpr);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(sdp_free);
+      if (warp == 0) SPA_TRACE_EV(4, it);
 
       // Row statistics of this iteration are in shared memory once group A's
       // 128 threads have arrived (bounded, unlike a bar.sync).
-      ok = warp_wait(row_ready, it & 1, wc, 305, it);
+      ok = warp_wait(row_ready, it & 1, wc, 9, it);
       if (!ok) break;
       const float* lse2 = row_buf + ((it & 1) * 2 + 0) * 64 + c_base;
       const float* dlt = row_buf + ((it & 1) * 2 + 1) * 64 + c_base;
@@ -410,20 +484,28 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
         dsp[2 * c4 + 1] = pack2<T>(dsv[2], dsv[3]);
       }
 
+      if (warp == 0) SPA_TRACE_EV(5, it);
       if (it > 0) {
         // dV/dK/dQ MMAs of the previous iteration have finished reading P^T/dS^T.
-        ok = warp_wait(mma_done, (it - 1) & 1, wc, 310, it);
+        ok = warp_wait(mma_done, (it - 1) & 1, wc, 10, it);
         if (!ok) break;
         tc_fence_after();
+      }
+      if (warp == 0) SPA_TRACE_EV(6, it);
+      if (p.tmem_ops) {
+        tmem_st16(t_p, pp);
+        tmem_st16(t_ds, dsp);
       }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const uint32_t off = sw128_chunk_off(r, grp * 4 + c);
-        *reinterpret_cast<uint4*>(p_row + off) =
-            make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
+        if (!p.tmem_ops)
+          *reinterpret_cast<uint4*>(p_row + off) =
+              make_uint4(pp[4 * c], pp[4 * c + 1], pp[4 * c + 2], pp[4 * c + 3]);
         *reinterpret_cast<uint4*>(ds_row + off) =
             make_uint4(dsp[4 * c], dsp[4 * c + 1], dsp[4 * c + 2], dsp[4 * c + 3]);
       }
+      if (p.tmem_ops) tmem_st_wait();
       if (grp == 0 && it + 1 < n_it) {
         row_buf[(((it + 1) & 1) * 2 + (r >> 6)) * 64 + (r & 63)] = next_stat;
         mbar_arrive(row_ready);
@@ -431,10 +513,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(pds_full);
+      if (warp == 0) SPA_TRACE_EV(7, it);
     }
 
     if (ok && n_it > 0) {
-      ok = warp_wait(mma_done, (n_it - 1) & 1, wc, 320, n_it);
+      ok = warp_wait(mma_done, (n_it - 1) & 1, wc, 11, n_it);
       if (ok) tc_fence_after();
     }
 
@@ -498,6 +581,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
     __syncthreads();
   }
+  if (p.prof && threadIdx.x < 32) {
+    if (threadIdx.x == 31) prof_s[31] = (unsigned long long)(clock64() - t_start);  // CTA lifetime
+    __syncwarp();
+    atomicAdd(&p.prof[threadIdx.x], prof_s[threadIdx.x]);
+  }
   if (warp == kWarpMma) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
@@ -522,11 +610,26 @@ int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
   p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.Hq = a->Hq; p.Hkv = a->Hkv;
   p.causal = a->causal; p.causal_off = a->causal_off;
   p.dkv_fp32 = a->dkv_fp32; p.dkv_accumulate = a->dkv_accumulate;
+  {
+    static int mode = -1;   // SPA_BWD_DRAIN=red selects per-thread reductions instead of TMA reduce-add
+    if (mode < 0) {
+      const char* e = getenv("SPA_BWD_DRAIN");
+      mode = (e && e[0] == 'r') ? 1 : 0;
+    }
+    p.drain_red = mode;
+    static int tm = -1;     // SPA_BWD_TMEM=0 feeds dV/dK from shared-memory operands instead of TMEM
+    if (tm < 0) {
+      const char* e = getenv("SPA_BWD_TMEM");
+      tm = (e && e[0] == '0') ? 0 : 1;
+    }
+    p.tmem_ops = tm;
+  }
   p.n_kvblk = ceil_div(a->Sk, kTileKV);
   p.scale = a->scale; p.scale_log2 = a->scale * kLog2e;
   p.lse = a->lse; p.delta = a->delta; p.dq_acc = a->dq_acc; p.dk = a->dk; p.dv = a->dv;
   p.status = device_status_word();
   if (!p.status) return SPA_ECUDA;
+  p.prof = wait_profile_buffer();   // nullptr unless SPA_WAIT_PROFILE=1
   const int smem_bytes = L::kTotal + 1024;
   auto kern = attn_bwd_sm100_kernel<D, T>;
   static bool attr_set = false;
@@ -549,6 +652,7 @@ int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
     set_error("bwd sm100 launch: %s", cudaGetErrorString(e));
     return SPA_ECUDA;
   }
+  if (p.prof) wait_profile_report("bwd", (cudaStream_t)a->stream);
   return SPA_OK;
 }
 

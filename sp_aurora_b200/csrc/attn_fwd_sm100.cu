@@ -13,8 +13,10 @@
 //   warp  8    TMA producer (lane 0)
 //   warp  9    tcgen05.mma issuer (lane 0); also owns the TMEM allocation
 // TMEM columns: S0 [0,128) S1 [128,256) O0 [256,256+D) O1 [256+D,256+2D).
-// Shared memory: Q (2 tiles), P (2 tiles, bf16/fp16 probabilities, K-major
-// 128B-swizzled so they feed the PV MMA as operand A), and a ring of K/V tiles.
+// The probabilities P (bf16/fp16, two per 32-bit column) overwrite the first 64
+// columns of their S tile and feed the PV MMA as operand A straight from TMEM:
+// P never goes through shared memory, whose bandwidth (128 B/clk) is what
+// bounds this kernel. Shared memory holds Q (2 tiles) and a ring of K/V tiles.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
@@ -45,20 +47,20 @@ struct FwdParams {
   float* out_acc;
   float* lse;
   int* status;
+  unsigned long long* prof;  // optional global array [32] of blocked cycles per wait site
 };
 
 template <int D>
 struct FwdSmem {
   static constexpr int kSlabBytes = kTileM * 128;           // 128 rows x 128 B
   static constexpr int kTileBytes = (D / 64) * kSlabBytes;   // one Q/K/V tile
-  static constexpr int kPBytes = 2 * kSlabBytes;             // 128 x 128 probabilities
-  static constexpr int kStages = (D == 128) ? 3 : 4;
+  static constexpr int kStages = (D == 128) ? 5 : 8;
   static constexpr int kQOff = 0;
-  static constexpr int kPOff = kQOff + 2 * kTileBytes;
-  static constexpr int kKVOff = kPOff + 2 * kPBytes;
+  static constexpr int kKVOff = kQOff + 2 * kTileBytes;
   static constexpr int kBarOff = kKVOff + kStages * kTileBytes;
   static constexpr int kNumBars = 1 + 2 * kStages + 6;
-  static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
+  static constexpr int kProfOff = kBarOff + kNumBars * 8 + 16;   // 32 x u64 wait profile
+  static constexpr int kTotal = kProfOff + 32 * 8;
 };
 
 template <typename T>
@@ -128,6 +130,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   }
   const int nmax = max(n_t[0], n_t[1]);
 
+  if (threadIdx.x < 32) reinterpret_cast<unsigned long long*>(smem + L::kProfOff)[threadIdx.x] = 0;
   if (threadIdx.x == 0) {
     *cta_abort = 0;
     mbar_init(q_full, 1);
@@ -151,7 +154,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  WaitCtx wc{p.status, cta_abort};
+  unsigned long long* prof_s = reinterpret_cast<unsigned long long*>(smem + L::kProfOff);
+  WaitCtx wc{p.status, cta_abort, p.prof ? prof_s : nullptr};
+  const long long t_start = clock64();
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA
@@ -169,7 +174,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       for (int n = 0; n < nfill; ++n) {
         const int slot = n % L::kStages;
         const uint32_t ph = (n / L::kStages) & 1;
-        if (!mbar_wait(&kv_empty[slot], ph ^ 1, wc, 100, n)) break;
+        if (!mbar_wait(&kv_empty[slot], ph ^ 1, wc, 0, n)) break;
         mbar_arrive_expect_tx(&kv_full[slot], L::kTileBytes);
         const CUtensorMap* tm = (n & 1) ? &tm_v : &tm_k;
         const int j = n >> 1;
@@ -180,67 +185,71 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA
-    if (lane == 0 && nmax > 0) {
+    // Every lane runs this code with identical values; only the tcgen05
+    // instructions are predicated on the leader lane.
+    if (nmax > 0) {
+      const uint32_t leader = lane == 0;
       constexpr uint32_t idesc_qk = make_idesc(128, 128, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc(128, D, kBf16, false, true);
       const uint32_t q_base = smem_u32(smem + L::kQOff);
-      const uint32_t p_base = smem_u32(smem + L::kPOff);
       const uint32_t kv_base = smem_u32(smem + L::kKVOff);
-      bool ok = mbar_wait(q_full, 0, wc, 200, 0);
+      bool ok = mbar_wait(q_full, 0, wc, 1, 0);
       tc_fence_after();
 
+      // Descriptors are built once; stepping through a tile only adds constants
+      // to the low word (the issuing thread is latency bound otherwise).
+      const SmemDesc q_desc = make_smem_desc(q_base, 16, 1024);
+      const SmemDesc k_desc = make_smem_desc(kv_base, 16, 1024);             // K-major
+      const SmemDesc v_desc = make_smem_desc(kv_base, L::kSlabBytes, 1024);  // MN-major
       // S_t = Q_t * K_j^T : A = Q (K-major), B = K tile (K-major).
       auto issue_qk = [&](int t, int j) -> bool {
         const int n = 2 * j;
         const int slot = n % L::kStages;
-        if (!mbar_wait(&kv_full[slot], (n / L::kStages) & 1, wc, 201, j)) return false;
+        if (!mbar_wait(&kv_full[slot], (n / L::kStages) & 1, wc, 2, j)) return false;
         tc_fence_after();
-        const uint32_t a0 = q_base + t * L::kTileBytes;
-        const uint32_t b0 = kv_base + slot * L::kTileBytes;
+        const uint32_t a0 = (t * L::kTileBytes) >> 4;
+        const uint32_t b0 = (slot * L::kTileBytes) >> 4;
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const uint32_t off = (kk / 4) * L::kSlabBytes + (kk % 4) * 32;
-          mma_ss(tmem_base + t * 128, smem_desc_sw128(a0 + off, 16, 1024),
-                 smem_desc_sw128(b0 + off, 16, 1024), idesc_qk, kk > 0);
+          const uint32_t off = ((kk / 4) * L::kSlabBytes + (kk % 4) * 32) >> 4;
+          mma_ss_u(tmem_base + t * 128, q_desc, a0 + off, k_desc, b0 + off, idesc_qk, kk > 0, leader);
         }
-        mma_commit(&s_full[t]);
+        mma_commit_u(&s_full[t], leader);
         return true;
       };
-      // O_t (+)= P_t * V_j : A = P (K-major over keys), B = V tile (MN-major:
-      // rows are keys = K dimension, D contiguous).
+      // O_t (+)= P_t * V_j : A = P read from TMEM (columns of S_t), B = V tile
+      // (MN-major: rows are keys = K dimension, D contiguous).
       auto issue_pv = [&](int t, int j) -> bool {
         const int n = 2 * j + 1;
         const int slot = n % L::kStages;
-        if (!mbar_wait(&kv_full[slot], (n / L::kStages) & 1, wc, 202, j)) return false;
+        if (!mbar_wait(&kv_full[slot], (n / L::kStages) & 1, wc, 3, j)) return false;
         tc_fence_after();
-        const uint32_t a0 = p_base + t * L::kPBytes;
-        const uint32_t b0 = kv_base + slot * L::kTileBytes;
+        const uint32_t b0 = (slot * L::kTileBytes) >> 4;
 #pragma unroll
-        for (int kk = 0; kk < kTileN / 16; ++kk) {
-          const uint32_t aoff = (kk / 4) * L::kSlabBytes + (kk % 4) * 32;
-          const uint32_t boff = kk * 2048;
-          mma_ss(tmem_base + 256 + t * D, smem_desc_sw128(a0 + aoff, 16, 1024),
-                 smem_desc_sw128(b0 + boff, L::kSlabBytes, 1024), idesc_pv, (j > 0 || kk > 0));
-        }
-        mma_commit(&o_done[t]);
+        for (int kk = 0; kk < kTileN / 16; ++kk)
+          mma_ts_u(tmem_base + 256 + t * D, tmem_base + t * 128 + kk * 8, v_desc,
+                   b0 + ((kk * 2048) >> 4), idesc_pv, (j > 0 || kk > 0), leader);
+        mma_commit_u(&o_done[t], leader);
         return true;
       };
 
       for (int t = 0; t < 2 && ok; ++t)
         if (n_t[t] > 0) ok = issue_qk(t, 0);
-      if (ok) mma_commit(&kv_empty[0]);  // K_0 slot free once both S(0) are done
+      if (ok) mma_commit_u(&kv_empty[0], leader);  // K_0 slot free once both S(0) are done
       for (int j = 0; j < nmax && ok; ++j) {
         for (int t = 0; t < 2 && ok; ++t) {
           if (j >= n_t[t]) continue;
-          ok = mbar_wait(&p_full[t], j & 1, wc, 203, j);
+          ok = mbar_wait(&p_full[t], j & 1, wc, 4, j);
           if (!ok) break;
           tc_fence_after();
-          if (j + 1 < n_t[t]) ok = issue_qk(t, j + 1);
-          if (ok) ok = issue_pv(t, j);
+          // PV(j) first: the pipe executes in order, so S(j+1) cannot overwrite
+          // the columns P(j) lives in before PV(j) has read them.
+          ok = issue_pv(t, j);
+          if (ok && j + 1 < n_t[t]) ok = issue_qk(t, j + 1);
         }
         if (!ok) break;
-        if (j + 1 < nmax) mma_commit(&kv_empty[(2 * j + 2) % L::kStages]);
-        mma_commit(&kv_empty[(2 * j + 1) % L::kStages]);
+        if (j + 1 < nmax) mma_commit_u(&kv_empty[(2 * j + 2) % L::kStages], leader);
+        mma_commit_u(&kv_empty[(2 * j + 1) % L::kStages], leader);
       }
     }
   } else {
@@ -252,7 +261,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t tmem_s = tmem_base + lane_field + t * 128;
     const uint32_t tmem_o = tmem_base + lane_field + 256 + t * D;
-    uint8_t* p_tile = smem + L::kPOff + t * L::kPBytes;
     const int nt = n_t[t];
     const int tile_row_min = q0 + t * kTileM;
     const float ninf = -INFINITY;
@@ -262,7 +270,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     bool ok = true;
 
     for (int j = 0; j < nt; ++j) {
-      ok = warp_wait(&s_full[t], j & 1, wc, 300 + t, j);
+      ok = warp_wait(&s_full[t], j & 1, wc, 8 + t, j);
       if (!ok) break;
       tc_fence_after();
       uint32_t sr[128];
@@ -310,7 +318,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
 
       if (j > 0) {
         // PV(j-1) must be complete before O is rescaled or P is overwritten.
-        ok = warp_wait(&o_done[t], (j - 1) & 1, wc, 310 + t, j);
+        ok = warp_wait(&o_done[t], (j - 1) & 1, wc, 10 + t, j);
         if (!ok) break;
         tc_fence_after();
         if (resc_any) {
@@ -327,21 +335,17 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
           tmem_st_wait();
         }
       }
-      // P row -> shared memory (K-major, 128B swizzle; 16 chunks of 8 values).
-#pragma unroll
-      for (int c = 0; c < 16; ++c) {
-        uint8_t* dst = p_tile + (c >> 3) * L::kSlabBytes + sw128_chunk_off(row_in_tile, c & 7);
-        *reinterpret_cast<uint4*>(dst) =
-            make_uint4(pk[4 * c], pk[4 * c + 1], pk[4 * c + 2], pk[4 * c + 3]);
-      }
-      fence_proxy_async_smem();
+      // P row -> TMEM, packed two per column, over the first 64 columns of S_t.
+      tmem_st32(tmem_s, pk);
+      tmem_st32(tmem_s + 32, pk + 32);
+      tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&p_full[t]);
     }
 
     // ------------------------------------------------------------- epilogue
     if (ok && nt > 0) {
-      ok = warp_wait(&o_done[t], (nt - 1) & 1, wc, 320 + t, nt);
+      ok = warp_wait(&o_done[t], (nt - 1) & 1, wc, 12 + t, nt);
       tc_fence_after();
     }
     if (ok) {
@@ -424,6 +428,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
     __syncthreads();
   }
+  if (p.prof && threadIdx.x < 32) {
+    if (threadIdx.x == 31) prof_s[31] = (unsigned long long)(clock64() - t_start);  // CTA lifetime
+    __syncwarp();
+    atomicAdd(&p.prof[threadIdx.x], prof_s[threadIdx.x]);
+  }
   if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
@@ -449,6 +458,7 @@ int launch_fwd_typed(const spa_fwd_args* a, int is_bf16) {
   p.out_acc = a->out_acc; p.lse = a->lse;
   p.status = device_status_word();
   if (!p.status) return SPA_ECUDA;
+  p.prof = wait_profile_buffer();   // nullptr unless SPA_WAIT_PROFILE=1
   const int smem_bytes = L::kTotal + 1024;
   auto kern = attn_fwd_sm100_kernel<D, T>;
   static bool attr_set = false;  // per instantiation
@@ -471,6 +481,7 @@ int launch_fwd_typed(const spa_fwd_args* a, int is_bf16) {
     set_error("fwd sm100 launch: %s", cudaGetErrorString(e));
     return SPA_ECUDA;
   }
+  if (p.prof) wait_profile_report("fwd", (cudaStream_t)a->stream);
   return SPA_OK;
 }
 

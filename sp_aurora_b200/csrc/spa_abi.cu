@@ -53,6 +53,40 @@ int* device_status_word() {
   return g_status[dev];
 }
 
+// ------------------------------------------------------------ wait profile
+static unsigned long long* g_prof = nullptr;
+unsigned long long* wait_profile_buffer() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("SPA_WAIT_PROFILE");
+    on = (e && e[0] == '1') ? 1 : 0;
+  }
+  if (!on) return nullptr;
+  if (!g_prof && cudaMalloc(&g_prof, 160 * sizeof(unsigned long long)) != cudaSuccess) return nullptr;
+  cudaMemset(g_prof, 0, 160 * sizeof(unsigned long long));
+  return g_prof;
+}
+void wait_profile_report(const char* tag, cudaStream_t stream) {
+  unsigned long long h[160];
+  cudaStreamSynchronize(stream);
+  if (cudaMemcpy(h, g_prof, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return;
+  fprintf(stderr, "[spa wait profile %s] cta_cycles_sum=%llu", tag, h[31]);
+  for (int i = 0; i < 31; ++i)
+    if (h[i]) fprintf(stderr, " s%d=%.3f", i, (double)h[i] / (double)(h[31] ? h[31] : 1));
+  fprintf(stderr, "\n");
+  if (h[32]) {   // timeline of block 0 (events x 8 iterations), relative to the first stamp
+    unsigned long long t0 = ~0ull;
+    for (int i = 32; i < 160; ++i)
+      if (h[i] && h[i] < t0) t0 = h[i];
+    for (int ev = 0; ev < 16; ++ev) {
+      if (!h[32 + ev * 8]) continue;
+      fprintf(stderr, "  ev%-2d", ev);
+      for (int i = 0; i < 8; ++i) fprintf(stderr, " %7lld", (long long)(h[32 + ev * 8 + i] - t0));
+      fprintf(stderr, "\n");
+    }
+  }
+}
+
 // ------------------------------------------------------- TMA descriptor encode
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,

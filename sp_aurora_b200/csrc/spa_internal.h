@@ -25,6 +25,12 @@ int encode_rows_map(CUtensorMap* map, const void* ptr, int is_bf16, int D, int64
 int encode_f32_rows_map(CUtensorMap* map, const void* ptr, int D, int64_t S, int H, int B,
                         int box_rows);
 
+// Debug aid (library built with -DSPA_PROFILE_WAITS and env SPA_WAIT_PROFILE=1): a zeroed device array of 32 counters that
+// the tensor-core kernels fill with cycles blocked per wait site, and a
+// synchronous dump of it to stderr. Returns nullptr when the aid is off.
+unsigned long long* wait_profile_buffer();
+void wait_profile_report(const char* tag, cudaStream_t stream);
+
 // Launchers (return a spa status code).
 int launch_fwd_sm100(const spa_fwd_args* a);
 int launch_bwd_sm100(const spa_bwd_args* a);

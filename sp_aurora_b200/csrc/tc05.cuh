@@ -56,6 +56,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 struct WaitCtx {
   int* status;            // global status word (4 ints)
   volatile int* cta_abort;  // shared-memory flag of this CTA
+  unsigned long long* prof;  // optional shared-memory array [32]: cycles blocked per wait site
 };
 
 #ifndef SPA_WAIT_BUDGET_CYCLES
@@ -68,11 +69,28 @@ struct WaitCtx {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w,
                                           int site, int iter) {
   if (*w.cta_abort) return false;
+#ifndef SPA_PROFILE_WAITS
+  // Fast path without reading the clock (a clock read before every wait costs
+  // ~15% of kernel time; the wait profile is a compile-time debugging option).
   if (mbar_try_wait(bar, parity)) return true;
   long long t0 = clock64();
+#else
+  long long t0 = clock64();
+  if (mbar_try_wait(bar, parity)) {   // try_wait may itself suspend the thread for a while
+    if (w.prof && (threadIdx.x & 31) == 0)
+      atomicAdd(&w.prof[site & 31], (unsigned long long)(clock64() - t0));
+    return true;
+  }
+#endif
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) {
+#ifdef SPA_PROFILE_WAITS
+      if (w.prof && (threadIdx.x & 31) == 0)
+        atomicAdd(&w.prof[site & 31], (unsigned long long)(clock64() - t0));
+#endif
+      return true;
+    }
     if ((++spins & 0x3ff) == 0) {
       if (*w.cta_abort) return false;
       if (*reinterpret_cast<volatile int*>(w.status) != 0) {
@@ -189,6 +207,20 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
   return d;
 }
 
+// The same descriptor split into its two 32-bit words, so that the issuing thread
+// can step through a tile by adding a (compile-time) constant to the low word
+// instead of rebuilding 64 bits per MMA: byte offset `off` -> lo + (off >> 4).
+struct SmemDesc {
+  uint32_t lo, hi;
+};
+__device__ __forceinline__ SmemDesc make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
+                                                   uint32_t sbo_bytes) {
+  SmemDesc d;
+  d.lo = ((saddr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+  d.hi = ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
+  return d;
+}
+
 // Instruction descriptor for tcgen05.mma kind::f16 with fp32 accumulation:
 //   bits 4-5 D format (1 = f32); bits 7-9 A format, bits 10-12 B format
 //   (0 = f16, 1 = bf16); bit 15 A is MN-major; bit 16 B is MN-major;
@@ -206,6 +238,71 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
       "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Same, operands given as split descriptors plus offsets in 16-byte units.
+__device__ __forceinline__ void mma_ss_d(uint32_t d_tmem, SmemDesc a, uint32_t a_off16, SmemDesc b,
+                                         uint32_t b_off16, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+      "r"(a.lo + a_off16), "r"(a.hi), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_d(uint32_t d_tmem, uint32_t a_tmem, SmemDesc b,
+                                         uint32_t b_off16, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Warp-uniform variants: every lane of the issuing warp executes the statement
+// with identical operands (so the compiler can keep descriptors in uniform
+// registers) and the instruction itself is predicated on `leader`.
+__device__ __forceinline__ void mma_ss_u(uint32_t d_tmem, SmemDesc a, uint32_t a_off16, SmemDesc b,
+                                         uint32_t b_off16, uint32_t idesc, uint32_t accumulate,
+                                         uint32_t leader) {
+  asm volatile(
+      "{\n\t.reg .pred p, lp;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\tsetp.ne.b32 lp, %7, 0;\n\t"
+      "@lp tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+      "r"(a.lo + a_off16), "r"(a.hi), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc), "r"(accumulate),
+      "r"(leader)
+      : "memory");
+}
+__device__ __forceinline__ void mma_ts_u(uint32_t d_tmem, uint32_t a_tmem, SmemDesc b,
+                                         uint32_t b_off16, uint32_t idesc, uint32_t accumulate,
+                                         uint32_t leader) {
+  asm volatile(
+      "{\n\t.reg .pred p, lp;\n\t.reg .b64 db;\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "setp.ne.b32 p, %5, 0;\n\tsetp.ne.b32 lp, %6, 0;\n\t"
+      "@lp tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc), "r"(accumulate), "r"(leader)
+      : "memory");
+}
+__device__ __forceinline__ void mma_commit_u(uint64_t* bar, uint32_t leader) {
+  asm volatile(
+      "{\n\t.reg .pred lp;\n\tsetp.ne.b32 lp, %1, 0;\n\t"
+      "@lp tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(
+          smem_u32(bar)),
+      "r"(leader)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]; A is read from tensor memory (rows = TMEM
+// lanes, 16-bit elements packed two per 32-bit column, 8 columns per K=16 step).
+__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Arrive on `bar` when every tcgen05 operation issued so far by this thread
@@ -247,6 +344,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
       "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
       "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
       "r"(r[30]), "r"(r[31]), "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%16], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15};" ::"r"(r[0]),
+      "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+      "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(taddr)
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() {

@@ -20,14 +20,15 @@ from ._lib import BwdArgs, FwdArgs, check, lib, stream_ptr
 _SUPPORTED_D = (32, 64, 128)
 
 # Optional per-kernel timing: when set to a dict, every forward/backward kernel
-# call appends a (start, end) CUDA-event pair, recorded on the launching stream,
-# under "fwd" / "bwd". Used by the benchmark; None (default) records nothing.
+# call appends (start event, end event, algorithmic FLOPs of the call), the events
+# recorded on the launching stream, under "fwd" / "bwd". Used by the benchmark;
+# None (default) records nothing.
 KERNEL_TIMERS = None
 
 
 class _Timed:
-    def __init__(self, name, device):
-        self.name, self.device = name, device
+    def __init__(self, name, device, flops=0.0):
+        self.name, self.device, self.flops = name, device, flops
 
     def __enter__(self):
         if KERNEL_TIMERS is not None:
@@ -39,8 +40,21 @@ class _Timed:
     def __exit__(self, *exc):
         if KERNEL_TIMERS is not None:
             self.end.record(torch.cuda.current_stream(self.device))
-            KERNEL_TIMERS.setdefault(self.name, []).append((self.start, self.end))
+            KERNEL_TIMERS.setdefault(self.name, []).append((self.start, self.end, self.flops))
         return False
+
+
+def attn_flops(B, Sq, Sk, Hq, D, causal, causal_off=0) -> float:
+    """Algorithmic forward FLOPs of one call: 4*B*Hq*D*(visible query-key pairs)."""
+    if not causal:
+        pairs = float(Sq) * Sk
+    else:   # query i sees clamp(i + off + 1, 0, Sk) keys
+        i_a = min(Sq, max(0, -causal_off))                 # first row with at least one key
+        i_b = min(Sq, max(i_a, Sk - causal_off - 1))       # first row that sees all Sk keys
+        n = i_b - i_a                                      # rows on the ramp
+        first = i_a + causal_off + 1
+        pairs = n * first + n * (n - 1) / 2.0 + (Sq - i_b) * float(Sk)
+    return 4.0 * B * Hq * D * pairs
 
 
 def check_unsupported_kwargs(dropout_p=0.0, window_size=(-1, -1), alibi_slopes=None, softcap=0.0):
@@ -121,7 +135,7 @@ def attn_fwd_step(q, k, v, softmax_scale: float, causal: bool, lse: torch.Tensor
     a.causal, a.causal_off, a.merge_prev = int(bool(causal)), int(causal_off), int(bool(merge_prev))
     a.scale = float(softmax_scale)
     a.stream = stream_ptr(q.device)
-    with _Timed("fwd", q.device):
+    with _Timed("fwd", q.device, attn_flops(B, Sq, Sk, Hq, D, causal, causal_off)):
         check(lib.spa_attn_fwd(C.byref(a)), "spa_attn_fwd")
 
 
@@ -183,7 +197,7 @@ def attn_bwd_step(q, k, v, dout, lse, delta, softmax_scale: float, causal: bool,
     a.causal, a.causal_off = int(bool(causal)), int(causal_off)
     a.scale = float(softmax_scale)
     a.stream = stream_ptr(q.device)
-    with _Timed("bwd", q.device):
+    with _Timed("bwd", q.device, 2.5 * attn_flops(B, Sq, Sk, Hq, D, causal, causal_off)):
         check(lib.spa_attn_bwd(C.byref(a)), "spa_attn_bwd")
 
 
