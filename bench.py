@@ -278,6 +278,26 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item())
 
+    # ---------------- compute-only time (exchanges replaced by local hand-offs) ----------------
+    exposed = None
+    if world > 1:
+        from sp_aurora_b200 import ring as ring_mod
+        ring_mod.RingComm.FAKE = True
+        step(q, kv, dout)
+        barrier()
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0.record()
+        for _ in range(args.steps):
+            step(q, kv, dout)
+        g1.record()
+        barrier()
+        ring_mod.RingComm.FAKE = False
+        t = torch.tensor([g0.elapsed_time(g1) / args.steps], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        nocomm_ms = float(t.item())
+        exposed = {"step_ms": ms, "compute_only_ms": nocomm_ms,
+                   "exposed_comm_frac": max(0.0, (ms - nocomm_ms) / ms)}
+
     total_flops = 3.5 * fwd_flops(args.seq)
     value = total_flops / (ms * 1e-3) / 1e12
     peaks, peak_kind = load_peaks()
@@ -317,6 +337,7 @@ def main():
                     "h2d_bytes_per_step": int(world * (hq.numel() + hkv.numel() + hdo.numel()) * 2),
                     "d2h_bytes_per_step": int(world * host_res.numel() * 4)},
             "gpu_launches": int(launches),
+            "exposed_comm": exposed,
             "clocks": clocks,
         }
         if not args.no_cpu_baseline and world == 1:

@@ -41,6 +41,11 @@ class RingComm:
     `wait`, `send_recv_kv`). All transfers queued by `send_recv` go out as one
     batched NCCL group at `commit()`; no even/odd ordering is needed."""
 
+    # Measurement aid: when True, exchanges are replaced by a local hand-off of
+    # the send buffer (results are wrong, kernel work and launch order are
+    # unchanged), which gives the compute-only time of a step.
+    FAKE = False
+
     def __init__(self, process_group: Optional[dist.ProcessGroup] = None):
         self._process_group = process_group
         self._ops: List[dist.P2POp] = []
@@ -60,6 +65,8 @@ class RingComm:
         if not to_send.is_contiguous():
             raise ValueError("RingComm.send_recv needs a contiguous tensor")
         res = torch.empty_like(to_send) if recv_tensor is None else recv_tensor
+        if RingComm.FAKE:
+            return to_send
         self._ops.append(dist.P2POp(dist.isend, to_send, self.send_rank, group=self._process_group))
         self._ops.append(dist.P2POp(dist.irecv, res, self.recv_rank, group=self._process_group))
         return res

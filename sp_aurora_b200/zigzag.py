@@ -49,6 +49,12 @@ def exchange_halves(pairs: Sequence[Tuple[List[torch.Tensor], List[torch.Tensor]
     to_zigzag=True : src_halves[i] is half-chunk 2r+i, dst_halves[j] receives slot j.
     to_zigzag=False: src_halves[j] is slot j, dst_halves[i] receives half-chunk 2r+i.
     All transfers of all pairs go out as one batched group (ordered per peer)."""
+    from .ring import RingComm
+    if RingComm.FAKE:          # measurement aid: local copies only, no transfers
+        for src, dst in pairs:
+            for i in range(2):
+                dst[i].copy_(src[i])
+        return
     r, W = _group_info(group)
     ops = []
     local = []
