@@ -226,10 +226,9 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
   } else if (warp == kWarpMma) {
     // ------------------------------------------------------------------ MMA
-    // Every lane runs this code with identical values; only the tcgen05
-    // instructions are predicated on the leader lane.
-    if (n_it > 0) {
-      const uint32_t leader = lane == 0;
+    // One elected lane issues every MMA (measured faster than predicated
+    // warp-uniform issue); descriptors are precomputed, offsets are constants.
+    if (lane == 0 && n_it > 0) {
       constexpr uint32_t idesc_sdp = make_idesc(128, kTileQ, kBf16, false, false);
       constexpr uint32_t idesc_dkv = make_idesc(128, D, kBf16, false, true);
       constexpr uint32_t idesc_dq = make_idesc(128, kTileQ, kBf16, true, true);
@@ -250,43 +249,50 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       const SmemDesc p_km = make_smem_desc(p_base, 16, 1024);        // P^T (shared-memory variant)
       const SmemDesc ds_km = make_smem_desc(ds_base, 16, 1024);      // dS^T as A of dK
       const SmemDesc ds_mn = make_smem_desc(ds_base, 16, 1024);      // dS^T as B of dQ^T
-      auto issue_sdp = [&](int it) -> bool {
-        const int slot = it % kStages;
+      // `slot` is a compile-time constant at every call site (the iteration loop is
+      // unrolled over the ring period): runtime descriptor words cost issue time.
+      auto issue_sdp = [&](int it, const int slot) -> bool {
         if (!mbar_wait(&qdo_full[slot], (it / kStages) & 1, wc, 2, it)) return false;
         tc_fence_after();
         const uint32_t qb = (slot * L::kStageBytes) >> 4;
         const uint32_t dob = qb + (L::kQTile >> 4);
+        SPA_TRACE_EV(11, it);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t aoff = ((kk / 4) * L::kKVSlab + (kk % 4) * 32) >> 4;
           const uint32_t boff = ((kk / 4) * L::kQSlab + (kk % 4) * 32) >> 4;
-          mma_ss_u(tmem_base + kColS, k_km, aoff, st_km, qb + boff, idesc_sdp, kk > 0, leader);
+          mma_ss_d(tmem_base + kColS, k_km, aoff, st_km, qb + boff, idesc_sdp, kk > 0);
         }
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t aoff = ((kk / 4) * L::kKVSlab + (kk % 4) * 32) >> 4;
           const uint32_t boff = ((kk / 4) * L::kQSlab + (kk % 4) * 32) >> 4;
-          mma_ss_u(tmem_base + kColDP, v_km, aoff, st_km, dob + boff, idesc_sdp, kk > 0, leader);
+          mma_ss_d(tmem_base + kColDP, v_km, aoff, st_km, dob + boff, idesc_sdp, kk > 0);
         }
-        mma_commit_u(sdp_full, leader);
+        SPA_TRACE_EV(12, it);
+        mma_commit(sdp_full);
         SPA_TRACE_EV(0, it);
         return true;
       };
 
-      if (ok) ok = issue_sdp(0);
-      for (int it = 0; it < n_it && ok; ++it) {
+      if (ok) ok = issue_sdp(0, 0);
+      for (int it0 = 0; it0 < n_it && ok; it0 += kStages) {
+#pragma unroll
+       for (int sl = 0; sl < kStages; ++sl) {
+        const int it = it0 + sl;
+        if (it >= n_it || !ok) break;
         if (it + 1 < n_it) {
           ok = mbar_wait(sdp_free, it & 1, wc, 3, it);
           if (!ok) break;
           tc_fence_after();
-          ok = issue_sdp(it + 1);
+          ok = issue_sdp(it + 1, (sl + 1) % kStages);
           if (!ok) break;
         }
         ok = mbar_wait(pds_full, it & 1, wc, 4, it);
         if (!ok) break;
         tc_fence_after();
         SPA_TRACE_EV(1, it);
-        const int slot = it % kStages;
+        const int slot = sl;
         const uint32_t qb = (slot * L::kStageBytes) >> 4;
         const uint32_t dob = qb + (L::kQTile >> 4);
         // dV += P^T dO ; dK += dS^T Q : B = dO / Q stage read MN-major; A = P^T / dS^T
@@ -294,36 +300,40 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
         if (p.tmem_ops) {
 #pragma unroll
           for (int kk = 0; kk < kTileQ / 16; ++kk)
-            mma_ts_u(tmem_base + kColDV, tmem_base + kColP + kk * 8, st_mn, dob + ((kk * 2048) >> 4),
-                     idesc_dkv, (it > 0 || kk > 0), leader);
+            mma_ts_d(tmem_base + kColDV, tmem_base + kColP + kk * 8, st_mn, dob + ((kk * 2048) >> 4),
+                     idesc_dkv, (it > 0 || kk > 0));
 #pragma unroll
           for (int kk = 0; kk < kTileQ / 16; ++kk)
-            mma_ts_u(tmem_base + kColDK, tmem_base + kColDS + kk * 8, st_mn, qb + ((kk * 2048) >> 4),
-                     idesc_dkv, (it > 0 || kk > 0), leader);
+            mma_ts_d(tmem_base + kColDK, tmem_base + kColDS + kk * 8, st_mn, qb + ((kk * 2048) >> 4),
+                     idesc_dkv, (it > 0 || kk > 0));
         } else {
 #pragma unroll
           for (int kk = 0; kk < kTileQ / 16; ++kk)
-            mma_ss_u(tmem_base + kColDV, p_km, (kk * 32) >> 4, st_mn, dob + ((kk * 2048) >> 4),
-                     idesc_dkv, (it > 0 || kk > 0), leader);
+            mma_ss_d(tmem_base + kColDV, p_km, (kk * 32) >> 4, st_mn, dob + ((kk * 2048) >> 4),
+                     idesc_dkv, (it > 0 || kk > 0));
 #pragma unroll
           for (int kk = 0; kk < kTileQ / 16; ++kk)
-            mma_ss_u(tmem_base + kColDK, ds_km, (kk * 32) >> 4, st_mn, qb + ((kk * 2048) >> 4),
-                     idesc_dkv, (it > 0 || kk > 0), leader);
+            mma_ss_d(tmem_base + kColDK, ds_km, (kk * 32) >> 4, st_mn, qb + ((kk * 2048) >> 4),
+                     idesc_dkv, (it > 0 || kk > 0));
         }
         // dQ^T = K^T dS : A = K tile read MN-major (M = head dim), B = dS^T tile
         // read MN-major (N = queries), contraction over the 128 keys.
+        SPA_TRACE_EV(13, it);
         if (it > 0) {
           ok = mbar_wait(dq_free, (it - 1) & 1, wc, 5, it);
           if (!ok) break;
           tc_fence_after();
         }
+        SPA_TRACE_EV(14, it);
 #pragma unroll
         for (int kk = 0; kk < kTileKV / 16; ++kk)
-          mma_ss_u(tmem_base + kColDQ, k_mn, (kk * 2048) >> 4, ds_mn, (kk * 2048) >> 4, idesc_dq,
-                   kk > 0, leader);
-        mma_commit_u(mma_done, leader);
+          mma_ss_d(tmem_base + kColDQ, k_mn, (kk * 2048) >> 4, ds_mn, (kk * 2048) >> 4, idesc_dq,
+                   kk > 0);
+        SPA_TRACE_EV(15, it);
+        mma_commit(mma_done);
         SPA_TRACE_EV(2, it);
-        mma_commit_u(&qdo_empty[slot], leader);
+        mma_commit(&qdo_empty[slot]);
+       }
       }
     }
   } else if (warp >= 8) {

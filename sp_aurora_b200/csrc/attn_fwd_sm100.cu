@@ -54,7 +54,7 @@ template <int D>
 struct FwdSmem {
   static constexpr int kSlabBytes = kTileM * 128;           // 128 rows x 128 B
   static constexpr int kTileBytes = (D / 64) * kSlabBytes;   // one Q/K/V tile
-  static constexpr int kStages = (D == 128) ? 5 : 8;
+  static constexpr int kStages = 4;   // K_j -> slots 0,2 ; V_j -> slots 1,3 (period of two key tiles)
   static constexpr int kQOff = 0;
   static constexpr int kKVOff = kQOff + 2 * kTileBytes;
   static constexpr int kBarOff = kKVOff + kStages * kTileBytes;
@@ -185,10 +185,9 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA
-    // Every lane runs this code with identical values; only the tcgen05
-    // instructions are predicated on the leader lane.
-    if (nmax > 0) {
-      const uint32_t leader = lane == 0;
+    // One elected lane issues every MMA (measured faster than predicated
+    // warp-uniform issue); descriptors are precomputed, offsets are constants.
+    if (lane == 0 && nmax > 0) {
       constexpr uint32_t idesc_qk = make_idesc(128, 128, kBf16, false, false);
       constexpr uint32_t idesc_pv = make_idesc(128, D, kBf16, false, true);
       const uint32_t q_base = smem_u32(smem + L::kQOff);
@@ -202,9 +201,10 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       const SmemDesc k_desc = make_smem_desc(kv_base, 16, 1024);             // K-major
       const SmemDesc v_desc = make_smem_desc(kv_base, L::kSlabBytes, 1024);  // MN-major
       // S_t = Q_t * K_j^T : A = Q (K-major), B = K tile (K-major).
-      auto issue_qk = [&](int t, int j) -> bool {
+      // `slot` is a compile-time constant at every call site (the key-tile loop is
+      // unrolled over the ring period): runtime descriptor words cost issue time.
+      auto issue_qk = [&](int t, int j, const int slot) -> bool {
         const int n = 2 * j;
-        const int slot = n % L::kStages;
         if (!mbar_wait(&kv_full[slot], (n / L::kStages) & 1, wc, 2, j)) return false;
         tc_fence_after();
         const uint32_t a0 = (t * L::kTileBytes) >> 4;
@@ -212,44 +212,51 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t off = ((kk / 4) * L::kSlabBytes + (kk % 4) * 32) >> 4;
-          mma_ss_u(tmem_base + t * 128, q_desc, a0 + off, k_desc, b0 + off, idesc_qk, kk > 0, leader);
+          mma_ss_d(tmem_base + t * 128, q_desc, a0 + off, k_desc, b0 + off, idesc_qk, kk > 0);
         }
-        mma_commit_u(&s_full[t], leader);
+        mma_commit(&s_full[t]);
         return true;
       };
       // O_t (+)= P_t * V_j : A = P read from TMEM (columns of S_t), B = V tile
       // (MN-major: rows are keys = K dimension, D contiguous).
-      auto issue_pv = [&](int t, int j) -> bool {
+      auto issue_pv = [&](int t, int j, const int slot) -> bool {
         const int n = 2 * j + 1;
-        const int slot = n % L::kStages;
         if (!mbar_wait(&kv_full[slot], (n / L::kStages) & 1, wc, 3, j)) return false;
         tc_fence_after();
         const uint32_t b0 = (slot * L::kTileBytes) >> 4;
 #pragma unroll
         for (int kk = 0; kk < kTileN / 16; ++kk)
-          mma_ts_u(tmem_base + 256 + t * D, tmem_base + t * 128 + kk * 8, v_desc,
-                   b0 + ((kk * 2048) >> 4), idesc_pv, (j > 0 || kk > 0), leader);
-        mma_commit_u(&o_done[t], leader);
+          mma_ts_d(tmem_base + 256 + t * D, tmem_base + t * 128 + kk * 8, v_desc,
+                   b0 + ((kk * 2048) >> 4), idesc_pv, (j > 0 || kk > 0));
+        mma_commit(&o_done[t]);
         return true;
       };
 
-      for (int t = 0; t < 2 && ok; ++t)
-        if (n_t[t] > 0) ok = issue_qk(t, 0);
-      if (ok) mma_commit_u(&kv_empty[0], leader);  // K_0 slot free once both S(0) are done
-      for (int j = 0; j < nmax && ok; ++j) {
-        for (int t = 0; t < 2 && ok; ++t) {
-          if (j >= n_t[t]) continue;
-          ok = mbar_wait(&p_full[t], j & 1, wc, 4, j);
+      static_assert(L::kStages == 4, "slot constants below assume a 4-stage ring");
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+        if (ok && n_t[t] > 0) ok = issue_qk(t, 0, 0);
+      if (ok) mma_commit(&kv_empty[0]);  // K_0 slot free once both S(0) are done
+      for (int j0 = 0; j0 < nmax && ok; j0 += 2) {
+#pragma unroll
+        for (int jj = 0; jj < 2; ++jj) {
+          const int j = j0 + jj;
+          if (j >= nmax || !ok) break;
+#pragma unroll
+          for (int t = 0; t < 2; ++t) {
+            if (!ok || j >= n_t[t]) continue;
+            ok = mbar_wait(&p_full[t], j & 1, wc, 4, j);
+            if (!ok) break;
+            tc_fence_after();
+            // PV(j) first: the pipe executes in order, so S(j+1) cannot overwrite
+            // the columns P(j) lives in before PV(j) has read them.
+            ok = issue_pv(t, j, 2 * jj + 1);
+            if (ok && j + 1 < n_t[t]) ok = issue_qk(t, j + 1, (2 * jj + 2) % 4);
+          }
           if (!ok) break;
-          tc_fence_after();
-          // PV(j) first: the pipe executes in order, so S(j+1) cannot overwrite
-          // the columns P(j) lives in before PV(j) has read them.
-          ok = issue_pv(t, j);
-          if (ok && j + 1 < n_t[t]) ok = issue_qk(t, j + 1);
+          if (j + 1 < nmax) mma_commit(&kv_empty[(2 * jj + 2) % 4]);
+          mma_commit(&kv_empty[2 * jj + 1]);
         }
-        if (!ok) break;
-        if (j + 1 < nmax) mma_commit_u(&kv_empty[(2 * j + 2) % L::kStages], leader);
-        mma_commit_u(&kv_empty[(2 * j + 1) % L::kStages], leader);
       }
     }
   } else {
