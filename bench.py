@@ -120,6 +120,53 @@ def cpu_reference_sample(seq=4096, steps=1, threads=None):
     return 3.5 * fwd_flops(seq) / best / 1e12, best, threads
 
 
+def run_aux(args):
+    """`--aux`: achieved HBM bandwidth of the bandwidth-bound helper kernels
+    (Ulysses pack/unpack permutation, stand-alone merge, delta, fp32->bf16 cast) on
+    cfg3-sized tensors, against the measured copy bandwidth. One JSON line."""
+    import sp_aurora_b200 as spa
+    from sp_aurora_b200 import all_to_all as a2a, local_attn as la
+    torch.cuda.set_device(0)
+    peaks, kind = load_peaks()
+    peak = peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])
+    Bq, S, H, Dh, P = 2, 8192, 32, 128, 8          # cfg3: one rank's [2, 8192, 32, 128] bf16 shard
+    x = torch.randn(Bq, S, H, Dh, device="cuda").bfloat16()
+    send = torch.empty((P, Bq, S, H // P, Dh), dtype=x.dtype, device="cuda")
+    src = x.unflatten(2, (P, H // P)).permute(2, 0, 1, 3, 4)
+    outp = torch.empty((Bq, S, H, Dh), dtype=x.dtype, device="cuda")
+    acc = torch.randn(Bq, S, H, Dh, device="cuda")
+    lse = torch.randn(Bq, H, S, device="cuda")
+    blse = torch.randn(Bq, H, S, device="cuda")
+    nbytes = x.numel() * 2
+
+    def timeit(fn, n=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e-3
+
+    res = {}
+    for name, fn, traffic in (
+            ("permute_rows pack (seq->head, 256 B rows)", lambda: a2a.strided_copy(send, src), 2 * nbytes),
+            ("permute_rows unpack (head->seq)", lambda: a2a.strided_copy(outp.view(Bq, S, P, H // P, Dh),
+                                                                          send.permute(1, 2, 0, 3, 4)), 2 * nbytes),
+            ("merge (fp32 acc r/w + bf16 block)", lambda: la.update_out_and_lse(acc, lse, x, blse),
+             x.numel() * (4 + 4 + 2)),
+            ("delta (rowsum dO*O)", lambda: la.bwd_delta(x, x), 2 * nbytes),
+            ("cast fp32->bf16", lambda: la.cast_from_f32(acc, torch.bfloat16, 1.0, outp), x.numel() * 6)):
+        t = timeit(fn)
+        res[name] = {"ms": t * 1e3, "algorithmic_GBps": traffic / t / 1e9, "frac_of_peak": traffic / t / 1e9 / peak}
+    spa.check_status()
+    print(json.dumps({"aux_kernels": res, "peak_GBps": peak, "peak_source": kind + " hbm_gbs",
+                      "tensor": [Bq, S, H, Dh], "dtype": "bf16", "note": "inputs 134 MB > L2"}), flush=True)
+
+
 def run_reference(args, rank, world):
     """`--impl reference`: the reference's CPU attention math (oracle port) on
     the host cores; rank 0 only, each step a bounded sample of the workload."""
@@ -183,6 +230,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--seq", type=int, default=DEFAULT_SEQ)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--aux", action="store_true", help="bandwidth of the HBM-bound helper kernels")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -190,6 +238,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.aux:
+        run_aux(args)
         return
 
     import sp_aurora_b200 as spa

@@ -440,7 +440,16 @@ int spa_attn_bwd(const spa_bwd_args* a) {
   int rc = validate_common(a->B, a->Sq, a->Sk, a->Hq, a->Hkv, a->D, a->dtype, a->scale);
   if (rc) return rc;
   const bool tensor_core = a->dtype != SPA_DTYPE_F32 && a->D != 32 && !force_simt();
-  rc = tensor_core ? launch_bwd_sm100(a) : launch_bwd_simt(a);
+  if (tensor_core) {
+    static int wide = -1;   // SPA_BWD128=1 selects the (slower, experimental) 128x128-tile kernel
+    if (wide < 0) {
+      const char* e = getenv("SPA_BWD128");
+      wide = (e && e[0] == '1') ? 1 : 0;
+    }
+    rc = (a->D == 128 && wide) ? launch_bwd128_sm100(a) : launch_bwd_sm100(a);
+  } else {
+    rc = launch_bwd_simt(a);
+  }
   if (rc == SPA_OK) note_launch(tensor_core ? 1 : 2);
   return rc;
 }

@@ -111,6 +111,24 @@ def _worker(rank, world, port, ret):
             e = _errs([(out, ro[:, sl])])
             el = _errs([(lse, rl[:, :, sl])])[0]
             res[tag] = (e[0] <= 2e-2 and el <= 1e-3, e, el)
+        # ---- hybrid module with separate q,k,v and gradients (U x R = 2 x world/2 when possible)
+        U = 2 if world % 2 == 0 and world > 2 else world
+        R = world // U
+        spa.destroy_seq_parallel_pg()
+        spa.set_seq_parallel_pg(U, R, rank, world)
+        B, S, H, D = 1, 1024, 4, 128
+        q, k, v, do = (_rand((B, S, H, D), 20 + i).bfloat16() for i in range(4))
+        ro, rl = orc.attention_ref(q, k, v, None, True)
+        rdq, rdk, rdv = orc.attention_bwd_ref(do, q, k, v, ro, rl, None, True)
+        sl = sl_of(S)
+        ql, kl, vl = (t[:, sl].to(dev).requires_grad_(True) for t in (q, k, v))
+        mod = spa.LongContextAttention()
+        out = mod(ql, kl, vl, causal=True)
+        out.backward(do[:, sl].to(dev))
+        spa.check_status()
+        e = _errs([(out, ro[:, sl]), (ql.grad, rdq[:, sl]), (kl.grad, rdk[:, sl]), (vl.grad, rdv[:, sl])])
+        gmax = max(1.0, float(rdv.abs().max()) / 4)
+        res["hyb_bwd"] = (e[0] <= 2e-2 and max(e[1:]) <= 2e-2 * gmax, e, 0.0)
         spa.destroy_seq_parallel_pg()
     except Exception:  # noqa: BLE001
         res["error"] = traceback.format_exc()
@@ -135,7 +153,7 @@ def results():
 
 
 @pytest.mark.parametrize("tag", ["ring_fp32", "ring_bf16_gqa", "ring_bf16_gqa_contig", "ring_bf16_noncausal", "uly_b2",
-                                 "uly_gqa_causal", "a2a_exact", "hyb_u", "hyb_r"])
+                                 "uly_gqa_causal", "a2a_exact", "hyb_u", "hyb_r", "hyb_bwd"])
 def test_multi_gpu_parity(results, tag):
     for r, res in results.items():
         ok, errs, el = res[tag]

@@ -176,3 +176,27 @@ def test_large_shape_against_cuda_core_kernel(spa):
     ro, rl = orc.attention_ref(q[:, rows].cpu(), k.cpu(), v.cpu(), None, True, causal_off=3000)
     assert (out[:, rows].cpu().double() - ro).abs().max() <= 2e-2
     assert (lse[:, :, rows].cpu().double() - rl).abs().max() <= 1e-3
+
+
+def test_wide_tile_backward_variant_in_subprocess():
+    """The experimental 128x128-tile backward (SPA_BWD128=1, read once per process)
+    must give the same gradients as the default kernel."""
+    import subprocess
+    import sys
+    code = (
+        "import os, sys, torch; sys.path.insert(0, %r);"
+        "import sp_aurora_b200 as spa; from oracle import attention_oracle as orc;"
+        "g = torch.Generator().manual_seed(3);"
+        "q, k, v, do = (torch.randn(1, 384, 2, 128, generator=g).bfloat16() for _ in range(4));"
+        "ro, rl = orc.attention_ref(q, k, v, None, True);"
+        "r = orc.attention_bwd_ref(do, q, k, v, ro, rl, None, True);"
+        "out, lse = spa.flash_attn_forward(q.cuda(), k.cuda(), v.cuda(), None, True);"
+        "got = spa.flash_attn_backward(do.cuda(), q.cuda(), k.cuda(), v.cuda(), out, lse, None, True);"
+        "spa.check_status();"
+        "errs = [float((a.cpu().double() - b).abs().max()) for a, b in zip(got, r)];"
+        "lim = 2e-2 * max(1.0, float(r[2].abs().max()) / 4);"
+        "assert max(errs) <= lim, errs; print('ok', errs)"
+    ) % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, SPA_BWD128="1")
+    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stdout + res.stderr
