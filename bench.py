@@ -129,7 +129,7 @@ def run_aux(args):
     torch.cuda.set_device(0)
     peaks, kind = load_peaks()
     peak = peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])
-    Bq, S, H, Dh, P = 2, 8192, 32, 128, 8          # cfg3: one rank's [2, 8192, 32, 128] bf16 shard
+    Bq, S, H, Dh, P = args.aux_batch, 8192, 32, 128, 8   # batch 2 = cfg3: one rank's [2,8192,32,128] bf16 shard
     x = torch.randn(Bq, S, H, Dh, device="cuda").bfloat16()
     send = torch.empty((P, Bq, S, H // P, Dh), dtype=x.dtype, device="cuda")
     src = x.unflatten(2, (P, H // P)).permute(2, 0, 1, 3, 4)
@@ -164,7 +164,8 @@ def run_aux(args):
         res[name] = {"ms": t * 1e3, "algorithmic_GBps": traffic / t / 1e9, "frac_of_peak": traffic / t / 1e9 / peak}
     spa.check_status()
     print(json.dumps({"aux_kernels": res, "peak_GBps": peak, "peak_source": kind + " hbm_gbs",
-                      "tensor": [Bq, S, H, Dh], "dtype": "bf16", "note": "inputs 134 MB > L2"}), flush=True)
+                      "tensor": [Bq, S, H, Dh], "dtype": "bf16",
+                      "note": f"inputs {nbytes >> 20} MiB > L2"}), flush=True)
 
 
 def run_reference(args, rank, world):
@@ -231,6 +232,7 @@ def main():
     ap.add_argument("--seq", type=int, default=DEFAULT_SEQ)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--aux", action="store_true", help="bandwidth of the HBM-bound helper kernels")
+    ap.add_argument("--aux-batch", type=int, default=2, help="batch of the --aux tensors (16 = 1 GiB)")
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

@@ -224,22 +224,60 @@ __device__ __forceinline__ RowIdx decode_row(long long row, int S, int H) {
   return r;
 }
 
+// 8 elements (16 bytes for 2-byte types) per thread; D/8 consecutive threads share a row.
+template <typename T>
+__device__ __forceinline__ float dot8(const T* a, const T* b);
+template <>
+__device__ __forceinline__ float dot8<float>(const float* a, const float* b) {
+  const float4 a0 = *reinterpret_cast<const float4*>(a), a1 = *reinterpret_cast<const float4*>(a + 4);
+  const float4 b0 = *reinterpret_cast<const float4*>(b), b1 = *reinterpret_cast<const float4*>(b + 4);
+  return a0.x * b0.x + a0.y * b0.y + a0.z * b0.z + a0.w * b0.w + a1.x * b1.x + a1.y * b1.y +
+         a1.z * b1.z + a1.w * b1.w;
+}
+template <>
+__device__ __forceinline__ float dot8<__nv_bfloat16>(const __nv_bfloat16* a, const __nv_bfloat16* b) {
+  const uint4 ua = *reinterpret_cast<const uint4*>(a), ub = *reinterpret_cast<const uint4*>(b);
+  const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wa[i]));
+    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wb[i]));
+    acc = fmaf(x.x, y.x, acc);
+    acc = fmaf(x.y, y.y, acc);
+  }
+  return acc;
+}
+template <>
+__device__ __forceinline__ float dot8<__half>(const __half* a, const __half* b) {
+  const uint4 ua = *reinterpret_cast<const uint4*>(a), ub = *reinterpret_cast<const uint4*>(b);
+  const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&wa[i]));
+    const float2 y = __half22float2(*reinterpret_cast<const __half2*>(&wb[i]));
+    acc = fmaf(x.x, y.x, acc);
+    acc = fmaf(x.y, y.y, acc);
+  }
+  return acc;
+}
+
 template <typename T>
 __global__ void delta_kernel(const T* __restrict__ out, int64_t o_sb, int64_t o_ss, int64_t o_sh,
                              const T* __restrict__ dout, int64_t d_sb, int64_t d_ss, int64_t d_sh,
                              float* __restrict__ delta, int B, int S, int H, int D) {
-  const int tpr = D / 4;
+  const int tpr = D / 8;
   const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long row = gid / tpr;
-  const int c = (int)(gid % tpr) * 4;
+  const int c = (int)(gid % tpr) * 8;
   const long long nrows = (long long)B * S * H;
   float acc = 0.f;
   RowIdx r = {0, 0, 0};
   if (row < nrows) {
     r = decode_row(row, S, H);
-    const float4 a = ld4<T>(out + r.b * o_sb + r.s * o_ss + r.h * o_sh + c);
-    const float4 d = ld4<T>(dout + r.b * d_sb + r.s * d_ss + r.h * d_sh + c);
-    acc = a.x * d.x + a.y * d.y + a.z * d.z + a.w * d.w;
+    acc = dot8<T>(out + r.b * o_sb + r.s * o_ss + r.h * o_sh + c,
+                  dout + r.b * d_sb + r.s * d_ss + r.h * d_sh + c);
   }
   for (int o = tpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
   if (row < nrows && c == 0) delta[((size_t)r.b * H + r.h) * S + r.s] = acc;
@@ -469,7 +507,7 @@ int spa_bwd_delta(const void* out, int64_t o_sb, int64_t o_ss, int64_t o_sh, con
     set_error("spa_bwd_delta: bad argument");
     return SPA_EINVAL;
   }
-  const long long threads = (long long)B * S * H * (D / 4);
+  const long long threads = (long long)B * S * H * (D / 8);
   const int block = 256;
   const long long grid = (threads + block - 1) / block;
   SPA_DISPATCH_T(dtype, delta_kernel<T><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
