@@ -168,6 +168,88 @@ def run_aux(args):
                       "note": f"inputs {nbytes >> 20} MiB > L2"}), flush=True)
 
 
+def run_other_workload(args, rank, world, local_rank):
+    """`--workload ulysses` (cfg3: B=2, total S=65536, H=32, D=128, non-causal, fwd+bwd) and
+    `--workload hybrid` (cfg5: qkv-packed B=1, total S=262144, H=16, D=128, causal, forward
+    only with lse; Ulysses degree min(4, N) inside, ring across). Same timing rules as the
+    default workload; one JSON line on rank 0."""
+    import sp_aurora_b200 as spa
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    ul = args.workload == "ulysses"
+    Bw, S, H = (2, 65536, 32) if ul else (1, 262144, 16)
+    if args.seq != DEFAULT_SEQ:
+        S = args.seq
+    sl = S // world
+    g = torch.Generator().manual_seed(777 + rank)
+    if ul:
+        q, k, v, do = (torch.randn(Bw, sl, H, D, generator=g).bfloat16().to(device) for _ in range(4))
+        for t in (q, k, v):
+            t.requires_grad_(True)
+        flops = 3.5 * 4.0 * Bw * H * float(S) * S * D
+
+        def step():
+            q.grad = k.grad = v.grad = None
+            out = spa.ulysses_flash_attn_func(q, k, v, causal=False)
+            out.backward(do)
+        name = "cfg3: Ulysses attention fwd+bwd (ulysses_flash_attn_func)"
+        par = f"ulysses{world}"
+    else:
+        qkv = torch.randn(Bw, sl, 3, H, D, generator=g).bfloat16().to(device)
+        U = min(4, world)
+        while world % U:
+            U -= 1
+        if world > 1:
+            spa.set_seq_parallel_pg(U, world // U, rank, world)
+        mod = spa.LongContextAttentionQKVPacked()
+        flops = 4.0 * Bw * H * float(S) * S * D / 2
+
+        def step():
+            with torch.no_grad():
+                mod(qkv, causal=True, return_attn_probs=True)
+        name = "cfg5: hybrid Ulysses x ring forward with lse (LongContextAttentionQKVPacked)"
+        par = f"ulysses{U}xring{world // U}" if world > 1 else "local"
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = spa.launch_count()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    launches = spa.launch_count() - l0
+    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    spa.check_status()
+    peaks, kind = load_peaks()
+    if rank == 0:
+        value = flops / (ms * 1e-3) / 1e12
+        print(json.dumps({
+            "metric": "attn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": name, "batch": Bw, "total_seq": S, "heads": H, "head_dim": D,
+                       "parallelism": par},
+            "tflops_per_gpu": value / world,
+            "pct_of_bf16_peak_sustained": 100.0 * value / world / peaks.get("bf16_tflops_sustained", 1400.0),
+            "tokens_per_s": Bw * S / (ms * 1e-3), "gpu_launches": int(launches)}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_reference(args, rank, world):
     """`--impl reference`: the reference's CPU attention math (oracle port) on
     the host cores; rank 0 only, each step a bounded sample of the workload."""
@@ -231,6 +313,7 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--seq", type=int, default=DEFAULT_SEQ)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="ring", choices=["ring", "ulysses", "hybrid"])
     ap.add_argument("--aux", action="store_true", help="bandwidth of the HBM-bound helper kernels")
     ap.add_argument("--aux-batch", type=int, default=2, help="batch of the --aux tensors (16 = 1 GiB)")
     args = ap.parse_args()
@@ -243,6 +326,9 @@ def main():
         return
     if args.aux:
         run_aux(args)
+        return
+    if args.workload != "ring":
+        run_other_workload(args, rank, world, local_rank)
         return
 
     import sp_aurora_b200 as spa
