@@ -467,6 +467,9 @@ def main():
                          "achieved": achieved, "peak": peak_sust, "unit": "TFLOP/s",
                          "frac": (achieved / peak_sust) if achieved else None,
                          "peak_source": f"{peak_kind} bf16_tflops_sustained", "traffic": None,
+                         "traffic_note": "ncu at S=16384 (profiles/): 3.3 GB DRAM per backward launch of "
+                                         "5.5 TFLOP, 6 % of HBM peak; not proportional to FLOPs, so not "
+                                         "scaled to this size",
                          "avg_launch_ms": avg_bwd, "launches_timed": n_bwd,
                          "flops_per_launch": bwd_flops_per_launch,
                          "fwd_kernel": {"avg_launch_ms": avg_fwd, "launches_timed": n_fwd,
