@@ -164,6 +164,31 @@ int encode_f32_rows_map(CUtensorMap* map, const void* ptr, int D, int64_t S, int
   return 0;
 }
 
+int encode_f32_slab_map(CUtensorMap* map, const void* ptr, int D, int64_t S, int H, int B,
+                        int box_rows) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) {
+    set_error("cuTensorMapEncodeTiled entry point not available");
+    return -1;
+  }
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)H * D * 4, (cuuint64_t)D * 4, (cuuint64_t)S * H * D * 4};
+  cuuint32_t box[4] = {32u, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if ((uintptr_t)ptr & 15) {
+    set_error("fp32 gradient buffer must be 16-byte aligned for TMA");
+    return -1;
+  }
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(ptr), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_error("cuTensorMapEncodeTiled(fp32 slab) failed with code %d", (int)r);
+    return -1;
+  }
+  return 0;
+}
+
 // ---------------------------------------------------------------- helpers
 namespace {
 

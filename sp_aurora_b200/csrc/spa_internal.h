@@ -25,6 +25,12 @@ int encode_rows_map(CUtensorMap* map, const void* ptr, int is_bf16, int D, int64
 int encode_f32_rows_map(CUtensorMap* map, const void* ptr, int D, int64_t S, int H, int B,
                         int box_rows);
 
+// Same tensor, box of `box_rows` sequence rows by 32 floats with the 128-byte swizzle:
+// shared-memory slabs of [box_rows][128 B] that a thread per row fills without bank
+// conflicts. Used to store or reduce-add dK/dV tiles.
+int encode_f32_slab_map(CUtensorMap* map, const void* ptr, int D, int64_t S, int H, int B,
+                        int box_rows);
+
 // Debug aid (library built with -DSPA_PROFILE_WAITS and env SPA_WAIT_PROFILE=1): a zeroed device array of 32 counters that
 // the tensor-core kernels fill with cycles blocked per wait site, and a
 // synchronous dump of it to stderr. Returns nullptr when the aid is off.

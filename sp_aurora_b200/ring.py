@@ -178,35 +178,35 @@ def ring_flash_attn_backward(process_group, dout, q, k, v, out, softmax_lse, sof
 
     cur, axis = _pack_kv(k, v)
     kv_bufs = [torch.empty_like(cur), torch.empty_like(cur)]
-    # fp32 travelling partials, K|V gradients as one message [2,B,S,Hkv,D]
-    dkv_bufs = [torch.empty((2, B, S, Hkv, D), dtype=torch.float32, device=q.device)
-                for _ in range(2)]
-    dkv_cur = None
+    # fp32 travelling partials, K|V gradients as one message [2,B,S,Hkv,D]. Each step's
+    # kernel writes into `local`; the partial that arrived with this K|V block is folded
+    # in after the kernel, so its transfer overlaps the kernel instead of preceding it.
+    local = torch.empty((2, B, S, Hkv, D), dtype=torch.float32, device=q.device)
+    dkv_bufs = [torch.empty_like(local) for _ in range(2)]
     next_dkv = None
     for step in range(W):
         nxt = None
         if step + 1 != W:
             nxt = kv_comm.send_recv(cur, kv_bufs[step % 2])
             kv_comm.commit()
-        if step <= r or not causal:
+        computed = step <= r or not causal
+        if computed:
             kc, vc = (k, v) if step == 0 else _split_kv(cur, axis)
-            if step == 0:
-                dkv_cur = dkv_bufs[0]
-                accumulate = False
-            else:
-                d_kv_comm.wait()
-                dkv_cur = next_dkv
-                accumulate = True
+            tgt = dkv_bufs[0] if step == 0 else local     # step 0 starts the travelling sum
             bwd_step(q, kc, vc, dout, softmax_lse, delta, softmax_scale, causal and step == 0,
-                     dq_acc, dkv_cur[0], dkv_cur[1], dkv_accumulate=accumulate)
-        elif step != 0:
+                     dq_acc, tgt[0], tgt[1], dkv_accumulate=False)
+        if step == 0:
+            send = dkv_bufs[0]
+        else:
             d_kv_comm.wait()
-            dkv_cur = next_dkv
+            send = next_dkv
+            if computed:
+                send.add_(local)
         if nxt is not None:
             kv_comm.wait()
             cur = nxt
-        recv = dkv_bufs[1] if dkv_cur is dkv_bufs[0] else dkv_bufs[0]
-        next_dkv = d_kv_comm.send_recv(dkv_cur, recv)
+        recv = dkv_bufs[1] if send is dkv_bufs[0] else dkv_bufs[0]
+        next_dkv = d_kv_comm.send_recv(send, recv)
         d_kv_comm.commit()
     d_kv_comm.wait()
     if q.dtype == torch.float32:
@@ -236,7 +236,8 @@ class RingFlashAttnFunc(torch.autograd.Function):
         local_attn.check_qkv(q, k, v)
         ctx.zigzag = _use_zigzag(group, q, causal)
         if ctx.zigzag:
-            out, lse, saved = zigzag.zigzag_ring_forward(group, q, k, v, softmax_scale)
+            out, lse, saved = zigzag.zigzag_ring_forward(group, q, k, v, softmax_scale,
+                                                         need_lse=bool(return_softmax))
             ctx.save_for_backward(*saved)
         else:
             out, lse = ring_flash_attn_forward(group, q, k, v, softmax_scale, causal)

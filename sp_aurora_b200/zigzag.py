@@ -106,7 +106,7 @@ def _step_calls(step: int, r: int, W: int):
 
 def zigzag_ring_forward(group, q, k, v, softmax_scale: float,
                         fwd_step: Callable = local_attn.attn_fwd_step,
-                        cast_fn: Callable = local_attn.cast_from_f32):
+                        cast_fn: Callable = local_attn.cast_from_f32, need_lse: bool = True):
     """Causal ring forward over contiguous shards with internal zigzag balance.
     Returns (out [B,S,Hq,D], lse [B,Hq,S], saved) with `saved` = zigzag-layout
     tensors for the backward (q_z, kv_z, out_z, lse_z)."""
@@ -149,15 +149,19 @@ def zigzag_ring_forward(group, q, k, v, softmax_scale: float,
             cur = nxt
 
     out = torch.empty((B, S, Hq, D), dtype=dt, device=dev)
-    lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
     o_dst = [torch.empty((B, h, Hq, D), dtype=dt, device=dev) for _ in range(2)]
-    l_dst = [torch.empty((B, Hq, h), dtype=torch.float32, device=dev) for _ in range(2)]
-    exchange_halves([([out_z[0], out_z[1]], o_dst), ([lse_z[0], lse_z[1]], l_dst)], group,
-                    to_zigzag=False)
+    pairs = [([out_z[0], out_z[1]], o_dst)]
+    lse = None
+    if need_lse:     # the backward uses lse_z; the contiguous lse is only for the caller
+        lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
+        l_dst = [torch.empty((B, Hq, h), dtype=torch.float32, device=dev) for _ in range(2)]
+        pairs.append(([lse_z[0], lse_z[1]], l_dst))
+    exchange_halves(pairs, group, to_zigzag=False)
     out[:, :h].copy_(o_dst[0])
     out[:, h:].copy_(o_dst[1])
-    lse[:, :, :h].copy_(l_dst[0])
-    lse[:, :, h:].copy_(l_dst[1])
+    if need_lse:
+        lse[:, :, :h].copy_(l_dst[0])
+        lse[:, :, h:].copy_(l_dst[1])
     return out, lse, (q_z, kv_z, out_z, lse_z)
 
 
@@ -178,33 +182,39 @@ def zigzag_ring_backward(group, dout, q_z, kv_z, out_z, lse_z, softmax_scale: fl
     exchange_halves([(_halves(dout), [do_z[0], do_z[1]])], group, to_zigzag=True)
     delta_z = [delta_fn(out_z[i], do_z[i]) for i in range(2)]
     dq_acc = torch.zeros((2, B, h, Hq, D), dtype=torch.float32, device=dev)
-    dkv_bufs = [torch.empty((2, 2, B, h, Hkv, D), dtype=torch.float32, device=dev)
-                for _ in range(2)]
+    # dK|dV: each step's kernels write into `local`; the partial that travelled here
+    # with the K|V block is folded in AFTER the kernels (so its transfer overlaps
+    # them) and the sum is sent on. Layout [2(half), 2(k|v), B, h, Hkv, D] fp32.
+    local = torch.empty((2, 2, B, h, Hkv, D), dtype=torch.float32, device=dev)
+    dkv_bufs = [torch.empty_like(local) for _ in range(3)]
     kv_bufs = [torch.empty_like(kv_z), torch.empty_like(kv_z)]
     cur = kv_z
-    dkv_cur, next_dkv = None, None
+    next_dkv = None
     for step in range(W):
         nxt = None
         if step + 1 != W:
             nxt = kv_comm.send_recv(cur, kv_bufs[step % 2])
             kv_comm.commit()
-        if step == 0:
-            dkv_cur = dkv_bufs[0]
-            written = [False, False]
-        else:
-            d_kv_comm.wait()
-            dkv_cur = next_dkv
-            written = [True, True]
+        written = [False, False]
+        tgt = dkv_bufs[0] if step == 0 else local   # step 0 (both key halves) starts the sum
         for qh, kh, causal in _step_calls(step, r, W):
             bwd_step(q_z[qh], cur[kh, 0], cur[kh, 1], do_z[qh], lse_z[qh], delta_z[qh],
-                     softmax_scale, causal, dq_acc[qh], dkv_cur[kh, 0], dkv_cur[kh, 1],
+                     softmax_scale, causal, dq_acc[qh], tgt[kh, 0], tgt[kh, 1],
                      dkv_accumulate=written[kh])
             written[kh] = True
+        if step == 0:
+            send = dkv_bufs[0]
+        else:
+            d_kv_comm.wait()           # partial for this block, sent during the previous step
+            send = next_dkv
+            for kh in range(2):
+                if written[kh]:
+                    send[kh].add_(local[kh])
         if nxt is not None:
             kv_comm.wait()
             cur = nxt
-        recv = dkv_bufs[1] if dkv_cur is dkv_bufs[0] else dkv_bufs[0]
-        next_dkv = d_kv_comm.send_recv(dkv_cur, recv)
+        recv = dkv_bufs[(step + 1) % 3]
+        next_dkv = d_kv_comm.send_recv(send, recv)
         d_kv_comm.commit()
     d_kv_comm.wait()
 
