@@ -339,9 +339,6 @@ def main():
     device = torch.device("cuda", local_rank)
     group = None
     if world > 1:
-        # the ring moves 67-200 MB per step against milliseconds of compute: a few NCCL
-        # channels are plenty and leave the SMs to the attention kernels
-        os.environ.setdefault("NCCL_MAX_NCHANNELS", "4")
         dist.init_process_group("nccl", device_id=device)
     assert args.seq % (world * 256) == 0
 
