@@ -59,7 +59,6 @@ constexpr int kTileQ = 64;
 constexpr int kThreads = 448;
 constexpr int kWarpTma = 12, kWarpMma = 13;
 constexpr int kStages = 3;
-constexpr int kDefaultRedRows = 0;
 constexpr float kLog2e = 1.4426950408889634f;
 
 constexpr uint32_t kColS = 0, kColDP = 64, kColDV = 128, kColDK = 256, kColDQ = 384;
@@ -70,7 +69,6 @@ struct BwdParams {
   int causal, causal_off;
   int dkv_fp32, dkv_accumulate;
   int drain_red;   // 1: dQ leaves by per-thread red.global.add, 0: shared staging + TMA reduce
-  int red_rows;    // last rows of each 64-query dQ tile that bypass the staging (per-thread reductions)
   int tmem_ops;    // 1: P^T / dS^T feed dV / dK from TMEM, 0: from shared memory
   int n_kvblk;
   int q_split;     // CTAs sharing one K/V tile, each over a slice of the query tiles (dK/dV by atomics)
@@ -391,20 +389,6 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
         continue;
       }
-      // The bulk reduce-add drains shared memory at a fixed rate per SM, so the last
-      // red_rows queries of the tile go out in parallel as per-thread reductions
-      // (coalesced 128 bytes per warp) straight from the registers.
-      const int n_stage = 32 - p.red_rows;   // rows of v1 that are staged
-      if (p.red_rows > 0 && d < D) {
-        const int hq = g * G + it / n_q;
-        const int q0 = (i_start + it % n_q) * kTileQ;
-        float* base = p.dq_acc + (((size_t)b * p.Sq + q0 + 32) * p.Hq + hq) * D + d;
-        const size_t rs = (size_t)p.Hq * D;
-        const int nvalid = p.Sq - q0 - 32;
-#pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (i >= n_stage && i < nvalid) atomicAdd(base + i * rs, __uint_as_float(v1[i]) * p.scale);
-      }
       // staging buffer must have been read by the previous reduce
       ok = warp_wait(stage_free, (it & 1) ^ 1, wc, 17, it);
       if (!ok) break;
@@ -412,7 +396,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           stage[i * D + d] = __uint_as_float(v0[i]) * p.scale;
-          if (i < n_stage) stage[(32 + i) * D + d] = __uint_as_float(v1[i]) * p.scale;
+          stage[(32 + i) * D + d] = __uint_as_float(v1[i]) * p.scale;
         }
       }
       fence_proxy_async_smem();
@@ -744,13 +728,6 @@ int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
       mode = (e && e[0] == 'r') ? 1 : 0;
     }
     p.drain_red = mode;
-    static int rr = -1;     // SPA_BWD_RED_ROWS=n: rows of each dQ tile sent as per-thread reductions
-    if (rr < 0) {
-      const char* e = getenv("SPA_BWD_RED_ROWS");
-      rr = e ? atoi(e) : kDefaultRedRows;
-      if (rr < 0 || rr > 32 || (rr & 7)) rr = kDefaultRedRows;
-    }
-    p.red_rows = rr;
     static int tm = -1;     // SPA_BWD_TMEM=0 feeds dV/dK from shared-memory operands instead of TMEM
     if (tm < 0) {
       const char* e = getenv("SPA_BWD_TMEM");
@@ -758,7 +735,6 @@ int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
     }
     p.tmem_ops = tm;
   }
-  if (encode_f32_rows_map(&tdq, a->dq_acc, D, a->Sq, a->Hq, a->B, kTileQ - p.red_rows)) return SPA_ECUDA;
   p.n_kvblk = ceil_div(a->Sk, kTileKV);
   p.q_split = choose_q_split(a, (long long)p.n_kvblk * a->B * a->Hkv);
   p.scale = a->scale; p.scale_log2 = a->scale * kLog2e;

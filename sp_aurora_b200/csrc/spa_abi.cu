@@ -288,6 +288,18 @@ __device__ __forceinline__ float dot8<__half>(const __half* a, const __half* b) 
   return acc;
 }
 
+// The pack/unpack copy keeps kVecPerThread independent 16-byte accesses in flight per
+// thread (a block sweeps kVecPerThread coalesced runs of blockDim vectors) with the
+// streaming (evict-first) hint. The same unrolling made delta, merge and cast slower
+// (measured), so those stay one vector per thread.
+constexpr int kVecPerThread = 4;
+constexpr int kStreamBlock = 256;
+
+inline long long stream_grid(long long n_vec) {
+  const long long per_block = (long long)kStreamBlock * kVecPerThread;
+  return (n_vec + per_block - 1) / per_block;
+}
+
 template <typename T>
 __global__ void delta_kernel(const T* __restrict__ out, int64_t o_sb, int64_t o_ss, int64_t o_sh,
                              const T* __restrict__ dout, int64_t d_sb, int64_t d_ss, int64_t d_sh,
@@ -366,21 +378,41 @@ struct PermuteParams {
   int64_t vec_per_row;
   int64_t total_vec;
 };
-// Thread = one 16-byte vector; consecutive threads walk a row, then the next
-// logical row, so both sides see full-line accesses.
-__global__ void permute_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
-                                    const PermuteParams p) {
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total_vec; i += stride) {
-    const int64_t v = i % p.vec_per_row;
-    int64_t r = i / p.vec_per_row;
-    const int64_t i3 = r % p.n[3]; r /= p.n[3];
-    const int64_t i2 = r % p.n[2]; r /= p.n[2];
-    const int64_t i1 = r % p.n[1]; r /= p.n[1];
-    const int64_t i0 = r;
-    const int64_t so = i0 * p.ss[0] + i1 * p.ss[1] + i2 * p.ss[2] + i3 * p.ss[3] + v * 16;
-    const int64_t dof = i0 * p.ds[0] + i1 * p.ds[1] + i2 * p.ds[2] + i3 * p.ds[3] + v * 16;
-    *reinterpret_cast<uint4*>(dst + dof) = *reinterpret_cast<const uint4*>(src + so);
+// Thread = kVecPerThread 16-byte vectors; consecutive threads walk a row, then the next
+// logical row, so both sides see full-line accesses. Idx is the integer type of the
+// vector / row arithmetic: 32-bit whenever the vector count allows (the 64-bit
+// divisions of the general case cost more issue slots than the copy has to spare).
+template <typename Idx>
+__global__ void __launch_bounds__(kStreamBlock)
+permute_rows_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst,
+                    const PermuteParams p) {
+  const Idx vpr = (Idx)p.vec_per_row, n1 = (Idx)p.n[1], n2 = (Idx)p.n[2], n3 = (Idx)p.n[3];
+  const int64_t chunk = (int64_t)gridDim.x * blockDim.x * kVecPerThread;
+  for (int64_t base = (int64_t)blockIdx.x * blockDim.x * kVecPerThread; base < p.total_vec;
+       base += chunk) {
+    uint4 val[kVecPerThread];
+    int64_t dof[kVecPerThread];
+    bool ok[kVecPerThread];
+#pragma unroll
+    for (int u = 0; u < kVecPerThread; ++u) {
+      const int64_t i64 = base + (int64_t)u * blockDim.x + threadIdx.x;
+      ok[u] = i64 < p.total_vec;
+      const Idx i = (Idx)(ok[u] ? i64 : 0);
+      const Idx v = i % vpr;
+      Idx r = i / vpr;
+      const Idx i3 = r % n3; r /= n3;
+      const Idx i2 = r % n2; r /= n2;
+      const Idx i1 = r % n1; r /= n1;
+      const Idx i0 = r;
+      const int64_t so = (int64_t)i0 * p.ss[0] + (int64_t)i1 * p.ss[1] + (int64_t)i2 * p.ss[2] +
+                         (int64_t)i3 * p.ss[3] + (int64_t)v * 16;
+      dof[u] = (int64_t)i0 * p.ds[0] + (int64_t)i1 * p.ds[1] + (int64_t)i2 * p.ds[2] +
+               (int64_t)i3 * p.ds[3] + (int64_t)v * 16;
+      if (ok[u]) val[u] = __ldcs(reinterpret_cast<const uint4*>(src + so));
+    }
+#pragma unroll
+    for (int u = 0; u < kVecPerThread; ++u)
+      if (ok[u]) __stcs(reinterpret_cast<uint4*>(dst + dof[u]), val[u]);
   }
 }
 
@@ -603,13 +635,17 @@ int spa_permute_rows(const void* src, void* dst, const int64_t n[4], const int64
   }
   p.vec_per_row = row_bytes / 16;
   p.total_vec = rows * p.vec_per_row;
-  const int block = 256;
+  const int block = kStreamBlock;
   // A few waves of 148 SMs x 8 resident blocks; the kernel grid-strides.
-  int64_t grid = (p.total_vec + block - 1) / block;
+  int64_t grid = stream_grid(p.total_vec);
   const int64_t cap = 148 * 8 * 4;
   if (grid > cap) grid = cap;
-  permute_rows_kernel<<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>((const uint8_t*)src,
-                                                                          (uint8_t*)dst, p);
+  if (p.total_vec < (1ll << 31))
+    permute_rows_kernel<uint32_t><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
+        (const uint8_t*)src, (uint8_t*)dst, p);
+  else
+    permute_rows_kernel<int64_t><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
+        (const uint8_t*)src, (uint8_t*)dst, p);
   int rc = check_launch("permute_rows");
   if (rc == SPA_OK) note_launch();
   return rc;
