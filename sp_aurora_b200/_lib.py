@@ -102,27 +102,29 @@ _SIGNATURES = {
 }
 
 
-def _rebuild_if_stale() -> None:
+def _rebuild_if_stale() -> str:
     """Developer convenience: when a compiler is present and a source file is
     newer than the library, recompile before loading (never a fallback: without
-    nvcc a stale or missing library still fails below)."""
+    nvcc a stale or missing library still fails below). Returns the build error
+    text, if any, so that a missing library can be explained."""
     from . import build as _build   # plain build recipe, does not load the library
     if os.environ.get("SPA_LIB_PATH"):
-        return
+        return ""
     try:
         stale = _build._stale(_LIB_PATH, [_build.CSRC / s for s in _build.SOURCES] + _build.HEADERS)
         if stale:
             _build.build()
-    except RuntimeError:
-        pass
+    except RuntimeError as e:
+        return str(e)
+    return ""
 
 
 def _load() -> C.CDLL:
-    _rebuild_if_stale()
+    build_error = _rebuild_if_stale()
     if not _LIB_PATH.exists():
         raise ImportError(
-            f"{_LIB_PATH} is missing: build it with `python -m sp_aurora_b200.build` "
-            "(this package has no fallback path)")
+            f"{_LIB_PATH} is missing: build it with `python sp_aurora_b200/build.py` "
+            "(this package has no fallback path)" + (f"\nlast build attempt:\n{build_error}" if build_error else ""))
     lib = C.CDLL(str(_LIB_PATH))
     for name, (res, args) in _SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError if the .so does not export it

@@ -71,7 +71,6 @@ struct BwdParams {
   int drain_red;   // 1: dQ leaves by per-thread red.global.add, 0: shared staging + TMA reduce
   int tmem_ops;    // 1: P^T / dS^T feed dV / dK from TMEM, 0: from shared memory
   int n_kvblk;
-  int q_split;     // CTAs sharing one K/V tile, each over a slice of the query tiles (dK/dV by atomics)
   float scale, scale_log2;
   const float* lse;
   const float* delta;
@@ -98,7 +97,7 @@ struct BwdSmem {
   static constexpr int kDQOff = kDSOff + kPBytes;            // dQ staging fp32 [64][D]
   static constexpr int kRowOff = kDQOff + kTileQ * D * 4;    // lse2/delta [2][2][64] floats
   static constexpr int kBarOff = kRowOff + 2 * 2 * 64 * 4;
-  static constexpr int kNumBars = 1 + 2 * kStages + 9;
+  static constexpr int kNumBars = 1 + 2 * kStages + 8;
   static constexpr int kProfOff = kBarOff + kNumBars * 8 + 16;   // 32 x u64 wait profile
   static constexpr int kTotal = kProfOff + 32 * 8;
 };
@@ -122,9 +121,7 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
                       const __grid_constant__ CUtensorMap tm_k,
                       const __grid_constant__ CUtensorMap tm_v,
                       const __grid_constant__ CUtensorMap tm_do,
-                      const __grid_constant__ CUtensorMap tm_dq,
-                      const __grid_constant__ CUtensorMap tm_dk,
-                      const __grid_constant__ CUtensorMap tm_dv, const BwdParams p) {
+                      const __grid_constant__ CUtensorMap tm_dq, const BwdParams p) {
   using L = BwdSmem<D>;
   constexpr bool kBf16 = std::is_same<T, __nv_bfloat16>::value;
   extern __shared__ uint8_t smem_raw[];
@@ -142,7 +139,6 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint64_t* row_ready = dq_free + 1;
   uint64_t* stage_full = row_ready + 1;
   uint64_t* stage_free = stage_full + 1;
-  uint64_t* epi_full = stage_free + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* row_buf = reinterpret_cast<float*>(smem + L::kRowOff);  // [buf][lse2|delta][64]
@@ -150,31 +146,25 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // Work decode: query slice fastest, then kv heads, batch, and KV tiles in ascending
-  // order (under a causal mask the first tiles see the most queries: longest first).
+  // Work decode: K/V tiles fastest (ascending: under a causal mask the first tiles see
+  // the most queries, longest first), then kv heads, then batch. The CTAs resident at
+  // any time then walk the Q / dO / dQ tiles of the same query heads a few tiles apart,
+  // so one HBM fetch serves all of them from L2 (S=65536 non-causal: 584 -> 713 TFLOP/s
+  // against kv heads fastest, where only every Hkv-th CTA shares a stream).
   int w = blockIdx.x;
-  const int qs = w % p.q_split;
-  w /= p.q_split;
+  const int kvblk = w % p.n_kvblk;
+  w /= p.n_kvblk;
   const int g = w % p.Hkv;
-  w /= p.Hkv;
-  const int b = w % p.B;
-  w /= p.B;
-  const int kvblk = w;
+  const int b = w / p.Hkv;
   const int kv0 = kvblk * kTileKV;
   const int G = p.Hq / p.Hkv;
 
   // Query tiles that can see this K/V tile.
-  int i_end = (p.Sq + kTileQ - 1) / kTileQ;
+  const int i_end = (p.Sq + kTileQ - 1) / kTileQ;
   int i_start = 0;
   if (p.causal) {
     const long long first_q = (long long)kv0 - p.causal_off;  // smallest query index seeing kv0
     if (first_q > 0) i_start = (int)min((long long)i_end, first_q / kTileQ);
-  }
-  if (p.q_split > 1) {  // this CTA's slice of the visible query tiles
-    const int vis = i_end - i_start;
-    const int lo = i_start + (int)((long long)vis * qs / p.q_split);
-    i_end = i_start + (int)((long long)vis * (qs + 1) / p.q_split);
-    i_start = lo;
   }
   const int n_q = i_end - i_start;
   const int n_it = n_q * G;
@@ -195,7 +185,6 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     mbar_init(row_ready, 128);
     mbar_init(stage_full, 128);
     mbar_init(stage_free, 1);
-    mbar_init(epi_full, 256);
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -545,66 +534,10 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
 
     // ------------------------------------------------------------- epilogue
-    // dV and dK rows: group A handles head-dim columns [0, D/2), group B the rest.
-    constexpr int kHalfChunks = D / 64;  // 32-column chunks per group
-    if (p.dkv_fp32) {
-      // fp32 gradients leave through shared memory: each 32-column chunk is a
-      // [128 keys][128 B] slab in the 128-byte swizzle (thread = key row, conflict-free
-      // 16-byte stores) over the K/V tiles (dV) and the Q/dO ring (dK), all idle now;
-      // one thread then issues a bulk tensor store per slab, or a bulk reduce-add when
-      // the destination already holds a partial sum or is shared with other CTAs.
-      uint8_t* stg_dv = smem + L::kKOff;
-      uint8_t* stg_dk = smem + L::kStageOff;
-      if (ok) {
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-          const uint32_t taddr = which == 0 ? t_dv : t_dk;
-          uint8_t* stg = which == 0 ? stg_dv : stg_dk;
-#pragma unroll
-          for (int cc = 0; cc < kHalfChunks; ++cc) {
-            const int c = grp * kHalfChunks + cc;
-            float o[32];
-            if (n_it > 0) {
-              uint32_t v[32];
-              tmem_ld32(taddr + c * 32, v);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * (which == 0 ? 1.f : p.scale);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = 0.f;
-            }
-            uint8_t* row = stg + c * (kTileKV * 128) + r * 128;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              *reinterpret_cast<float4*>(row + ((j ^ (r & 7)) << 4)) =
-                  make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-          }
-        }
-      }
-      fence_proxy_async_smem();
-      mbar_arrive(epi_full);
-      if (threadIdx.x == 0) {
-        bool go = mbar_wait(epi_full, 0, wc, 19, 0);
-        go = go && !*cta_abort && !(p.q_split > 1 && n_it == 0);
-        if (go) {
-          const bool add = p.dkv_accumulate || p.q_split > 1;
-#pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            if (add) {
-              tma_reduce_add_4d(&tm_dv, stg_dv + c * (kTileKV * 128), c * 32, kv0, g, b);
-              tma_reduce_add_4d(&tm_dk, stg_dk + c * (kTileKV * 128), c * 32, kv0, g, b);
-            } else {
-              tma_store_4d(&tm_dv, stg_dv + c * (kTileKV * 128), c * 32, kv0, g, b);
-              tma_store_4d(&tm_dk, stg_dk + c * (kTileKV * 128), c * 32, kv0, g, b);
-            }
-          }
-          bulk_commit_group();
-          bulk_wait_all();
-        }
-      }
-    } else if (ok) {
+    // dV and dK rows: group A writes head-dim columns [0, D/2), group B the rest.
+    if (ok) {
       const size_t row_off = (((size_t)b * p.Sk + kidx) * p.Hkv + g) * D;
+      constexpr int kHalfChunks = D / 64;  // 32-column chunks per group
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
         const uint32_t taddr = which == 0 ? t_dv : t_dk;
@@ -624,17 +557,31 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
             for (int i = 0; i < 32; ++i) o[i] = 0.f;
           }
           if (!key_ok) continue;
-          T* drow = reinterpret_cast<T*>(dst_base) + row_off + c * 32;
-          if (p.dkv_accumulate) {
+          if (p.dkv_fp32) {
+            float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(dst_base) + row_off +
+                                                    c * 32);
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] += static_cast<float>(drow[i]);
+            for (int i = 0; i < 8; ++i) {
+              float4 x = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
+              if (p.dkv_accumulate) {
+                const float4 y = dst[i];
+                x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+              }
+              dst[i] = x;
+            }
+          } else {
+            T* drow = reinterpret_cast<T*>(dst_base) + row_off + c * 32;
+            if (p.dkv_accumulate) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) o[i] += static_cast<float>(drow[i]);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(drow);
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+              dst[i] = make_uint4(pack2<T>(o[8 * i], o[8 * i + 1]), pack2<T>(o[8 * i + 2], o[8 * i + 3]),
+                                  pack2<T>(o[8 * i + 4], o[8 * i + 5]),
+                                  pack2<T>(o[8 * i + 6], o[8 * i + 7]));
           }
-          uint4* dst = reinterpret_cast<uint4*>(drow);
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            dst[i] = make_uint4(pack2<T>(o[8 * i], o[8 * i + 1]), pack2<T>(o[8 * i + 2], o[8 * i + 3]),
-                                pack2<T>(o[8 * i + 4], o[8 * i + 5]),
-                                pack2<T>(o[8 * i + 6], o[8 * i + 7]));
         }
       }
     }
@@ -657,57 +604,11 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   }
 }
 
-// One CTA per (K/V tile, kv head, batch) leaves the last wave partly empty when that count
-// is a small non-multiple of the SM count (one CTA fits per SM). With fp32 dK/dV the query
-// tiles of a K/V tile can be shared by 2, 4 or 8 CTAs that reduce-add their parts:
-// take the smallest split whose wave efficiency reaches 95 %, else the most efficient.
-// Under a causal mask CTAs differ in length and are issued longest first, which already
-// fills the tail, so only grids of less than two waves are split there (measured:
-// S=8192, 32/8 heads: non-causal 742 -> 835 TFLOP/s with a split of 2, causal 809 -> 777).
-// SPA_BWD_QSPLIT=n forces n.
-int choose_q_split(const spa_bwd_args* a, long long base_grid) {
-  if (!a->dkv_fp32) return 1;
-  static int forced = -1;
-  if (forced < 0) {
-    const char* e = getenv("SPA_BWD_QSPLIT");
-    forced = e ? atoi(e) : 0;
-  }
-  const int q_tiles = ceil_div(a->Sq, kTileQ);
-  if (forced > 0) return forced > q_tiles ? (q_tiles > 0 ? q_tiles : 1) : forced;
-  static int n_sm = 0;
-  if (n_sm == 0) {
-    int dev = 0, v = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess ||
-        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
-      v = 148;
-    n_sm = v;
-  }
-  if (a->causal && base_grid >= 2ll * n_sm) return 1;
-  int best = 1;
-  double best_eff = 0.0;
-  for (int s = 1; s <= 8; s *= 2) {
-    if (s > 1 && q_tiles / s < 8) break;          // keep every slice long enough to pipeline
-    const long long ctas = base_grid * s;
-    const long long waves = (ctas + n_sm - 1) / n_sm;
-    const double eff = (double)ctas / ((double)waves * n_sm);
-    if (eff > best_eff + 1e-9) { best = s; best_eff = eff; }
-    if (eff >= 0.95) break;
-  }
-  return best;
-}
-
 template <int D, typename T>
 int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
   using L = BwdSmem<D>;
-  CUtensorMap tq, tk, tv, tdo, tdq, tdk, tdv;
+  CUtensorMap tq, tk, tv, tdo, tdq;
   if (encode_f32_rows_map(&tdq, a->dq_acc, D, a->Sq, a->Hq, a->B, kTileQ)) return SPA_ECUDA;
-  if (a->dkv_fp32) {
-    if (encode_f32_slab_map(&tdk, a->dk, D, a->Sk, a->Hkv, a->B, kTileKV)) return SPA_ECUDA;
-    if (encode_f32_slab_map(&tdv, a->dv, D, a->Sk, a->Hkv, a->B, kTileKV)) return SPA_ECUDA;
-  } else {
-    tdk = tdq;   // never used by the kernel
-    tdv = tdq;
-  }
   if (encode_rows_map(&tq, a->q, is_bf16, D, a->Sq, a->Hq, a->B, a->q_ss, a->q_sh, a->q_sb, kTileQ))
     return SPA_ECUDA;
   if (encode_rows_map(&tdo, a->dout, is_bf16, D, a->Sq, a->Hq, a->B, a->do_ss, a->do_sh, a->do_sb,
@@ -736,7 +637,6 @@ int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
     p.tmem_ops = tm;
   }
   p.n_kvblk = ceil_div(a->Sk, kTileKV);
-  p.q_split = choose_q_split(a, (long long)p.n_kvblk * a->B * a->Hkv);
   p.scale = a->scale; p.scale_log2 = a->scale * kLog2e;
   p.lse = a->lse; p.delta = a->delta; p.dq_acc = a->dq_acc; p.dk = a->dk; p.dv = a->dv;
   p.status = device_status_word();
@@ -753,21 +653,12 @@ int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
     }
     attr_set = true;
   }
-  const long long grid = (long long)p.n_kvblk * a->B * a->Hkv * p.q_split;
+  const long long grid = (long long)p.n_kvblk * a->B * a->Hkv;
   if (grid <= 0 || grid > 0x7fffffffll) {
     set_error("bwd grid out of range");
     return SPA_EINVAL;
   }
-  if (p.q_split > 1 && !a->dkv_accumulate) {   // the slices add into zeroed gradients
-    const size_t bytes = (size_t)a->B * a->Sk * a->Hkv * D * sizeof(float);
-    cudaError_t e = cudaMemsetAsync(a->dk, 0, bytes, (cudaStream_t)a->stream);
-    if (e == cudaSuccess) e = cudaMemsetAsync(a->dv, 0, bytes, (cudaStream_t)a->stream);
-    if (e != cudaSuccess) {
-      set_error("bwd sm100 memset: %s", cudaGetErrorString(e));
-      return SPA_ECUDA;
-    }
-  }
-  kern<<<(unsigned)grid, kThreads, smem_bytes, (cudaStream_t)a->stream>>>(tq, tk, tv, tdo, tdq, tdk, tdv, p);
+  kern<<<(unsigned)grid, kThreads, smem_bytes, (cudaStream_t)a->stream>>>(tq, tk, tv, tdo, tdq, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("bwd sm100 launch: %s", cudaGetErrorString(e));

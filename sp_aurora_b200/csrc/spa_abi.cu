@@ -541,7 +541,8 @@ int spa_attn_bwd(const spa_bwd_args* a) {
       const char* e = getenv("SPA_BWD128");
       wide = (e && e[0] == '1') ? 1 : 0;
     }
-    rc = (a->D == 128 && wide) ? launch_bwd128_sm100(a) : launch_bwd_sm100(a);
+    if (a->D == 128 && wide) rc = launch_bwd128_sm100(a);
+    else rc = a->dkv_fp32 ? launch_bwd_f32out_sm100(a) : launch_bwd_sm100(a);
   } else {
     rc = launch_bwd_simt(a);
   }

@@ -39,7 +39,8 @@ void wait_profile_report(const char* tag, cudaStream_t stream);
 
 // Launchers (return a spa status code).
 int launch_fwd_sm100(const spa_fwd_args* a);
-int launch_bwd_sm100(const spa_bwd_args* a);
+int launch_bwd_sm100(const spa_bwd_args* a);          // dK/dV in the input dtype
+int launch_bwd_f32out_sm100(const spa_bwd_args* a);   // fp32 dK/dV (ring steps)
 int launch_bwd128_sm100(const spa_bwd_args* a);   // head_dim 128, 128x128 tiles
 int launch_fwd_simt(const spa_fwd_args* a);
 int launch_bwd_simt(const spa_bwd_args* a);
