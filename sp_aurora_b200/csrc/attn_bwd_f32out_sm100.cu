@@ -78,6 +78,7 @@ struct BwdParams {
   int drain_red;   // 1: dQ leaves by per-thread red.global.add, 0: shared staging + TMA reduce
   int tmem_ops;    // 1: P^T / dS^T feed dV / dK from TMEM, 0: from shared memory
   int n_kvblk;
+  int chunk;       // K/V tiles per scheduling chunk (n_kvblk or 1)
   int q_split;     // CTAs sharing one K/V tile, each over a slice of the query tiles (dK/dV by atomics)
   float scale, scale_log2;
   const float* lse;
@@ -157,23 +158,20 @@ attn_bwd_f32out_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // Work decode: query slice fastest, then K/V tiles (ascending: under a causal mask the
-  // first tiles see the most queries, longest first), kv heads, batch: resident CTAs walk
-  // the Q / dO / dQ tiles of the same query heads and share them through L2.
+  // Work decode: K/V tiles of one chunk fastest, then kv heads, batch, chunks. The host
+  // picks the chunk: all tiles (CTAs resident together then walk the Q / dO / dQ tiles of
+  // the same query heads a few tiles apart and share every HBM fetch through L2:
+  // S=65536 non-causal 584 -> 743 TFLOP/s), or one tile for small causal problems, where
+  // longest-tile-first over all heads matters more (S=8192 causal: 807 vs 605).
   int w = blockIdx.x;
   const int qs = w % p.q_split;
   w /= p.q_split;
-#ifdef SPA_BWD_HEADS_FASTEST
+  const int kv_lo = w % p.chunk;
+  w /= p.chunk;
   const int g = w % p.Hkv;
   w /= p.Hkv;
   const int b = w % p.B;
-  const int kvblk = w / p.B;
-#else
-  const int kvblk = w % p.n_kvblk;
-  w /= p.n_kvblk;
-  const int g = w % p.Hkv;
-  const int b = w / p.Hkv;
-#endif
+  const int kvblk = (w / p.B) * p.chunk + kv_lo;
   const int kv0 = kvblk * kTileKV;
   const int G = p.Hq / p.Hkv;
 
@@ -750,6 +748,7 @@ int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
     p.tmem_ops = tm;
   }
   p.n_kvblk = ceil_div(a->Sk, kTileKV);
+  p.chunk = (!a->causal || p.n_kvblk >= 256) ? p.n_kvblk : 1;
   p.q_split = choose_q_split(a, (long long)p.n_kvblk * a->B * a->Hkv);
   p.scale = a->scale; p.scale_log2 = a->scale * kLog2e;
   p.lse = a->lse; p.delta = a->delta; p.dq_acc = a->dq_acc; p.dk = a->dk; p.dv = a->dv;

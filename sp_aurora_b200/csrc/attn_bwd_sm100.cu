@@ -71,6 +71,7 @@ struct BwdParams {
   int drain_red;   // 1: dQ leaves by per-thread red.global.add, 0: shared staging + TMA reduce
   int tmem_ops;    // 1: P^T / dS^T feed dV / dK from TMEM, 0: from shared memory
   int n_kvblk;
+  int chunk;       // K/V tiles per scheduling chunk (n_kvblk or 1)
   float scale, scale_log2;
   const float* lse;
   const float* delta;
@@ -146,16 +147,18 @@ attn_bwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // Work decode: K/V tiles fastest (ascending: under a causal mask the first tiles see
-  // the most queries, longest first), then kv heads, then batch. The CTAs resident at
-  // any time then walk the Q / dO / dQ tiles of the same query heads a few tiles apart,
-  // so one HBM fetch serves all of them from L2 (S=65536 non-causal: 584 -> 713 TFLOP/s
-  // against kv heads fastest, where only every Hkv-th CTA shares a stream).
+  // Work decode: K/V tiles of one chunk fastest, then kv heads, batch, chunks. The host
+  // picks the chunk: all tiles (CTAs resident together then walk the Q / dO / dQ tiles of
+  // the same query heads a few tiles apart and share every HBM fetch through L2:
+  // S=65536 non-causal 584 -> 743 TFLOP/s), or one tile for small causal problems, where
+  // longest-tile-first over all heads matters more (S=8192 causal: 807 vs 605).
   int w = blockIdx.x;
-  const int kvblk = w % p.n_kvblk;
-  w /= p.n_kvblk;
+  const int kv_lo = w % p.chunk;
+  w /= p.chunk;
   const int g = w % p.Hkv;
-  const int b = w / p.Hkv;
+  w /= p.Hkv;
+  const int b = w % p.B;
+  const int kvblk = (w / p.B) * p.chunk + kv_lo;
   const int kv0 = kvblk * kTileKV;
   const int G = p.Hq / p.Hkv;
 
@@ -637,6 +640,7 @@ int launch_bwd_typed(const spa_bwd_args* a, int is_bf16) {
     p.tmem_ops = tm;
   }
   p.n_kvblk = ceil_div(a->Sk, kTileKV);
+  p.chunk = (!a->causal || p.n_kvblk >= 256) ? p.n_kvblk : 1;
   p.scale = a->scale; p.scale_log2 = a->scale * kLog2e;
   p.lse = a->lse; p.delta = a->delta; p.dq_acc = a->dq_acc; p.dk = a->dk; p.dv = a->dv;
   p.status = device_status_word();

@@ -41,6 +41,7 @@ struct FwdParams {
   int B, Sq, Sk, Hq, Hkv;
   int causal, causal_off, merge_prev;
   int n_qblk;
+  int chunk;   // query blocks per scheduling chunk (n_qblk or 1)
   float scale_log2;
   void* out;
   int64_t o_sb, o_ss, o_sh;
@@ -100,14 +101,18 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
-  // Work decode: heads fastest (K/V tiles of a GQA group stay hot in L2), then
-  // batch, query blocks longest-first so causal work is balanced at the tail.
+  // Work decode: query blocks of one chunk fastest (longest first under a causal mask),
+  // then heads, batch, chunks. The host picks the chunk: all query blocks (CTAs resident
+  // together then stream the K/V of one kv head, which stays in L2: S=131072 causal
+  // 993 -> 1036 TFLOP/s), or one block for small causal problems, where
+  // longest-block-first over all heads matters more.
   int w = blockIdx.x;
+  const int q_lo = w % p.chunk;
+  w /= p.chunk;
   const int h = w % p.Hq;
   w /= p.Hq;
   const int b = w % p.B;
-  w /= p.B;
-  const int qblk = p.n_qblk - 1 - w;
+  const int qblk = p.n_qblk - 1 - ((w / p.B) * p.chunk + q_lo);
   const int hk = h / (p.Hq / p.Hkv);
   const int q0 = qblk * 2 * kTileM;
 
@@ -460,6 +465,7 @@ int launch_fwd_typed(const spa_fwd_args* a, int is_bf16) {
   p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.Hq = a->Hq; p.Hkv = a->Hkv;
   p.causal = a->causal; p.causal_off = a->causal_off; p.merge_prev = a->merge_prev;
   p.n_qblk = ceil_div(a->Sq, 2 * kTileM);
+  p.chunk = (!a->causal || p.n_qblk >= 256) ? p.n_qblk : 1;
   p.scale_log2 = a->scale * kLog2e;
   p.out = a->out; p.o_sb = a->o_sb; p.o_ss = a->o_ss; p.o_sh = a->o_sh;
   p.out_acc = a->out_acc; p.lse = a->lse;
