@@ -253,3 +253,30 @@ def test_backward_query_split_in_subprocess(split):
         env["SPA_BWD_QSPLIT"] = split
     res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stdout + res.stderr
+
+
+def test_long_sequence_slices_against_oracle(spa):
+    """S = 65536 causal GQA: the sizes at which both kernels switch to the
+    all-tiles-of-a-head work order. Row slices of out / lse / dq and the last key
+    tile of dk / dv are checked against the CPU oracle run on those rows only
+    (causal_off places the slice inside the full sequence)."""
+    B, S, Hq, Hkv, D = 1, 65536, 8, 2, 128
+    dt = torch.bfloat16
+    q, k, v, dout = (_rand(sh, dt, s, 0.5) for sh, s in (
+        ((B, S, Hq, D), 11), ((B, S, Hkv, D), 12), ((B, S, Hkv, D), 13), ((B, S, Hq, D), 14)))
+    qc, kc, vc, dc = (t.cuda() for t in (q, k, v, dout))
+    out, lse = spa.flash_attn_forward(qc, kc, vc, None, True)
+    dq, dk, dv = spa.flash_attn_backward(dc, qc, kc, vc, out, lse, None, True)
+    spa.check_status()
+    for r0 in (30000, S - 128):
+        rows = slice(r0, r0 + 128)
+        ro, rl = orc.attention_ref(q[:, rows], k, v, None, True, causal_off=r0)
+        assert (out[:, rows].cpu().double() - ro).abs().max() <= 2e-2
+        assert (lse[:, :, rows].cpu().double() - rl).abs().max() <= 1e-3
+        rdq, rdk, rdv = orc.attention_bwd_ref(dout[:, rows], q[:, rows], k, v, ro, rl, None, True,
+                                              causal_off=r0)
+        lim = 2e-2 * max(1.0, float(rdv.abs().max()) / 4)
+        assert (dq[:, rows].cpu().double() - rdq).abs().max() <= lim
+        if r0 == S - 128:   # only these rows see the last 128 keys: their dk/dv are complete
+            assert (dk[:, rows].cpu().double() - rdk[:, rows]).abs().max() <= lim
+            assert (dv[:, rows].cpu().double() - rdv[:, rows]).abs().max() <= lim
