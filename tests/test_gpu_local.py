@@ -210,22 +210,23 @@ from sp_aurora_b200 import local_attn as la
 from oracle import attention_oracle as orc
 g = torch.Generator().manual_seed(11)
 worst = 0.0
-for (Sq, Sk, Hq, Hkv, causal, off) in ((1024, 1024, 4, 2, True, 0), (1000, 700, 4, 1, False, 0),
-                                       (1024, 512, 2, 2, True, 256), (2048, 2048, 2, 1, True, 0),
-                                       (512, 1024, 2, 2, True, 0)):   # last K/V tiles see no query
-    q, do = (torch.randn(1, Sq, Hq, 128, generator=g).bfloat16() for _ in range(2))
-    k, v = (torch.randn(1, Sk, Hkv, 128, generator=g).bfloat16() for _ in range(2))
+for (Sq, Sk, Hq, Hkv, causal, off, D) in ((1024, 1024, 4, 2, True, 0, 128), (1000, 700, 4, 1, False, 0, 128),
+                                          (1024, 512, 2, 2, True, 256, 128), (2048, 2048, 2, 1, True, 0, 128),
+                                          (512, 1024, 2, 2, True, 0, 128),   # last K/V tiles see no query
+                                          (1024, 1024, 4, 2, True, 0, 64), (1000, 700, 2, 1, False, 0, 64)):
+    q, do = (torch.randn(1, Sq, Hq, D, generator=g).bfloat16() for _ in range(2))
+    k, v = (torch.randn(1, Sk, Hkv, D, generator=g).bfloat16() for _ in range(2))
     ro, rl = orc.attention_ref(q, k, v, None, causal, causal_off=off)
     rdq, rdk, rdv = orc.attention_bwd_ref(do, q, k, v, ro, rl, None, causal, causal_off=off)
     qc, kc, vc, dc = (t.cuda() for t in (q, k, v, do))
     lse = rl.float().cuda()
     delta = la.bwd_delta(ro.to(torch.bfloat16).cuda(), dc)
     for accumulate in (False, True):
-        dq = torch.zeros(1, Sq, Hq, 128, device="cuda")
+        dq = torch.zeros(1, Sq, Hq, D, device="cuda")
         base = 0.5 if accumulate else float("nan")      # overwrite mode must ignore old contents
-        dk = torch.full((1, Sk, Hkv, 128), base, device="cuda")
-        dv = torch.full((1, Sk, Hkv, 128), base, device="cuda")
-        la.attn_bwd_step(qc, kc, vc, dc, lse, delta, 128 ** -0.5, causal, dq, dk, dv,
+        dk = torch.full((1, Sk, Hkv, D), base, device="cuda")
+        dv = torch.full((1, Sk, Hkv, D), base, device="cuda")
+        la.attn_bwd_step(qc, kc, vc, dc, lse, delta, D ** -0.5, causal, dq, dk, dv,
                          dkv_accumulate=accumulate, causal_off=off)
         spa.check_status()
         add = 0.5 if accumulate else 0.0
@@ -233,7 +234,7 @@ for (Sq, Sk, Hq, Hkv, causal, off) in ((1024, 1024, 4, 2, True, 0), (1000, 700, 
                 float((dk.cpu().double() - add - rdk).abs().max()),
                 float((dv.cpu().double() - add - rdv).abs().max())]
         lim = 2e-2 * max(1.0, float(rdv.abs().max()) / 4)
-        assert max(errs) <= lim, (Sq, Sk, causal, off, accumulate, errs)
+        assert max(errs) <= lim, (Sq, Sk, causal, off, D, accumulate, errs)
         worst = max(worst, max(errs))
 print("ok", worst)
 """
