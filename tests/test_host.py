@@ -286,3 +286,23 @@ def test_zigzag_plan_is_balanced():
         for r in range(W):
             work = [sum(0.5 if c[2] else 1.0 for c in _step_calls(s, r, W)) for s in range(W)]
             assert work == [2.0] * W          # every rank, every step: two half-blocks
+
+
+def test_bench_reference_arm_prints_contract_line():
+    """`bench.py --impl reference` runs on host cores only (the oracle port on a bounded
+    sample) and prints one JSON line with the keys the bench contract names."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference",
+                          "--steps", "1", "--warmup", "0"], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("{")]
+    assert len(lines) == 1, res.stdout
+    d = json.loads(lines[0])
+    assert d["impl"] == "reference" and d["metric"] == "ring_attn_fwd_bwd_tflops"
+    assert d["unit"] == "TFLOP/s" and d["higher_is_better"] is True and d["value"] > 0
+    assert d["cpu_baseline"]["kind"] in ("port", "reference") and d["cpu_baseline"]["cores"] >= 1
+    assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
+    assert d["e2e"]["value"] == d["value"]
