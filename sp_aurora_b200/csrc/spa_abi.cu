@@ -240,12 +240,15 @@ __device__ __forceinline__ void st4<__half>(__half* p, float4 v) {
 struct RowIdx {
   int b, s, h;
 };
-__device__ __forceinline__ RowIdx decode_row(long long row, int S, int H) {
+// Idx is uint32_t whenever the thread count allows: the 64-bit divisions of the general
+// case cost more issue slots than these streaming kernels have to spare.
+template <typename Idx>
+__device__ __forceinline__ RowIdx decode_row(Idx row, int S, int H) {
   RowIdx r;
-  r.h = (int)(row % H);
-  row /= H;
-  r.s = (int)(row % S);
-  r.b = (int)(row / S);
+  r.h = (int)(row % (Idx)H);
+  row /= (Idx)H;
+  r.s = (int)(row % (Idx)S);
+  r.b = (int)(row / (Idx)S);
   return r;
 }
 
@@ -300,19 +303,19 @@ inline long long stream_grid(long long n_vec) {
   return (n_vec + per_block - 1) / per_block;
 }
 
-template <typename T>
+template <typename T, typename Idx>
 __global__ void delta_kernel(const T* __restrict__ out, int64_t o_sb, int64_t o_ss, int64_t o_sh,
                              const T* __restrict__ dout, int64_t d_sb, int64_t d_ss, int64_t d_sh,
                              float* __restrict__ delta, int B, int S, int H, int D) {
   const int tpr = D / 8;
-  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long row = gid / tpr;
-  const int c = (int)(gid % tpr) * 8;
-  const long long nrows = (long long)B * S * H;
+  const Idx gid = (Idx)blockIdx.x * blockDim.x + threadIdx.x;
+  const Idx row = gid / (Idx)tpr;
+  const int c = (int)(gid % (Idx)tpr) * 8;
+  const Idx nrows = (Idx)B * S * H;
   float acc = 0.f;
   RowIdx r = {0, 0, 0};
   if (row < nrows) {
-    r = decode_row(row, S, H);
+    r = decode_row<Idx>(row, S, H);
     acc = dot8<T>(out + r.b * o_sb + r.s * o_ss + r.h * o_sh + c,
                   dout + r.b * d_sb + r.s * d_ss + r.h * d_sh + c);
   }
@@ -320,20 +323,20 @@ __global__ void delta_kernel(const T* __restrict__ out, int64_t o_sb, int64_t o_
   if (row < nrows && c == 0) delta[((size_t)r.b * H + r.h) * S + r.s] = acc;
 }
 
-template <typename T>
+template <typename T, typename Idx>
 __global__ void merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse,
                              const T* __restrict__ bo, int64_t bo_sb, int64_t bo_ss, int64_t bo_sh,
                              const float* __restrict__ blse, int B, int S, int H, int D) {
   const int tpr = D / 4;
-  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long row = gid / tpr;
-  const int c = (int)(gid % tpr) * 4;
-  const long long nrows = (long long)B * S * H;
+  const Idx gid = (Idx)blockIdx.x * blockDim.x + threadIdx.x;
+  const Idx row = gid / (Idx)tpr;
+  const int c = (int)(gid % (Idx)tpr) * 4;
+  const Idx nrows = (Idx)B * S * H;
   const bool ok = row < nrows;
   float lse_new = 0.f;
   size_t li = 0;
   if (ok) {
-    const RowIdx r = decode_row(row, S, H);
+    const RowIdx r = decode_row<Idx>(row, S, H);
     li = ((size_t)r.b * H + r.h) * S + r.s;
     const float lo = lse[li], lb = blse[li];
     const float mx = fmaxf(lo, lb);
@@ -357,15 +360,15 @@ __global__ void merge_kernel(float* __restrict__ out_acc, float* __restrict__ ls
   if (ok && c == 0) lse[li] = lse_new;
 }
 
-template <typename T>
+template <typename T, typename Idx>
 __global__ void cast_kernel(const float* __restrict__ src, T* __restrict__ dst, int64_t d_sb,
                             int64_t d_ss, int64_t d_sh, int B, int S, int H, int D, float alpha) {
   const int tpr = D / 4;
-  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long row = gid / tpr;
-  const int c = (int)(gid % tpr) * 4;
-  if (row >= (long long)B * S * H) return;
-  const RowIdx r = decode_row(row, S, H);
+  const Idx gid = (Idx)blockIdx.x * blockDim.x + threadIdx.x;
+  const Idx row = gid / (Idx)tpr;
+  const int c = (int)(gid % (Idx)tpr) * 4;
+  if (row >= (Idx)B * S * H) return;
+  const RowIdx r = decode_row<Idx>(row, S, H);
   float4 v = *reinterpret_cast<const float4*>(src + (size_t)row * D + c);
   v.x *= alpha; v.y *= alpha; v.z *= alpha; v.w *= alpha;
   st4<T>(dst + r.b * d_sb + r.s * d_ss + r.h * d_sh + c, v);
@@ -568,7 +571,11 @@ int spa_bwd_delta(const void* out, int64_t o_sb, int64_t o_ss, int64_t o_sh, con
   const long long threads = (long long)B * S * H * (D / 8);
   const int block = 256;
   const long long grid = (threads + block - 1) / block;
-  SPA_DISPATCH_T(dtype, delta_kernel<T><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
+  const bool small = grid * block < (1ll << 31);
+  SPA_DISPATCH_T(dtype, if (small) delta_kernel<T, uint32_t><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
+                            (const T*)out, o_sb, o_ss, o_sh, (const T*)dout, do_sb, do_ss, do_sh,
+                            delta, B, S, H, D);
+                        else delta_kernel<T, long long><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
                             (const T*)out, o_sb, o_ss, o_sh, (const T*)dout, do_sb, do_ss, do_sh,
                             delta, B, S, H, D));
   int rc = check_launch("delta");
@@ -587,7 +594,11 @@ int spa_merge(float* out_acc, float* lse, const void* block_out, int64_t bo_sb, 
   const long long threads = (long long)B * S * H * (D / 4);
   const int block = 256;
   const long long grid = (threads + block - 1) / block;
-  SPA_DISPATCH_T(dtype, merge_kernel<T><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
+  const bool small = grid * block < (1ll << 31);
+  SPA_DISPATCH_T(dtype, if (small) merge_kernel<T, uint32_t><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
+                            out_acc, lse, (const T*)block_out, bo_sb, bo_ss, bo_sh, block_lse, B, S,
+                            H, D);
+                        else merge_kernel<T, long long><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
                             out_acc, lse, (const T*)block_out, bo_sb, bo_ss, bo_sh, block_lse, B, S,
                             H, D));
   int rc = check_launch("merge");
@@ -605,7 +616,10 @@ int spa_cast_from_f32(const float* src, void* dst, int64_t d_sb, int64_t d_ss, i
   const long long threads = (long long)B * S * H * (D / 4);
   const int block = 256;
   const long long grid = (threads + block - 1) / block;
-  SPA_DISPATCH_T(dtype, cast_kernel<T><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
+  const bool small = grid * block < (1ll << 31);
+  SPA_DISPATCH_T(dtype, if (small) cast_kernel<T, uint32_t><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
+                            src, (T*)dst, d_sb, d_ss, d_sh, B, S, H, D, alpha);
+                        else cast_kernel<T, long long><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
                             src, (T*)dst, d_sb, d_ss, d_sh, B, S, H, D, alpha));
   int rc = check_launch("cast");
   if (rc == SPA_OK) note_launch();
