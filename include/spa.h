@@ -7,7 +7,8 @@
  *
  * Tensors are [B, S, H, D] with the last dimension contiguous; the other
  * three strides are given in ELEMENTS so packed views (kv[:, :, 0], qkv[:, :, i])
- * are passed without a copy. lse/delta are fp32 [B, Hq, Sq] contiguous.
+ * are passed without a copy. lse/delta are fp32 [B, Hq, Sq], rows contiguous, with
+ * batch and head strides in elements (both zero = contiguous).
  *
  * Each entry point names the reference interface it stands in for
  * (paths are relative to the sp-aurora project root).
@@ -58,7 +59,8 @@ typedef struct spa_fwd_args {
   const void* v; int64_t v_sb, v_ss, v_sh;
   void* out;     int64_t o_sb, o_ss, o_sh;   /* may be NULL                       */
   float* out_acc;                            /* [B,Sq,Hq,D] contiguous, may be NULL */
-  float* lse;                                /* [B,Hq,Sq] contiguous              */
+  float* lse;                                /* [B,Hq,Sq], see lse_sb / lse_sh    */
+  int64_t lse_sb, lse_sh;                    /* lse strides in elements; 0,0 = contiguous */
   int32_t B, Sq, Sk, Hq, Hkv, D;
   int32_t dtype;
   int32_t causal;
@@ -92,25 +94,48 @@ int spa_bwd_delta(const void* out, int64_t o_sb, int64_t o_ss, int64_t o_sh,
  *           (intended algorithm: sp_aurora/ring_flash_attn.py:97-152).
  *
  * P = exp(scale * Q K^T + mask - lse);  dV = P^T dO;  dP = dO V^T;
- * dS = P * (dP - delta);  dQ += scale * dS K;  dK = scale * dS^T Q.
- * dq_acc (fp32 [B,Sq,Hq,D] contiguous) is ACCUMULATED into (the caller zeroes
- * it before the first ring step). dk/dv are [B,Sk,Hkv,D] contiguous, fp32 when
- * dkv_fp32 != 0 else element type `dtype`; with dkv_accumulate != 0 the block
- * result is added to what dk/dv already hold (the travelling ring partial,
- * sp_aurora/ring_flash_attn.py:139-141), otherwise it overwrites them.
+ * dS = P * (dP - delta);  dQ = scale * dS K;  dK = scale * dS^T Q.
+ *
+ * dQ: the block's dQ is combined with the running sum of earlier ring steps.
+ *   dq_overwrite == 0: total = dq_acc + dQ (dq_acc holds the earlier steps' sum);
+ *   dq_overwrite != 0: total = dQ (dq_acc is not read and need not be initialised).
+ *   The total is written to dq (element type `dtype`, strided) if dq is non-NULL and
+ *   to dq_acc (fp32 [B,Sq,Hq,D] contiguous) if dq_acc is non-NULL. At least one of the
+ *   two is required; dq_acc is required when dq_overwrite == 0.
+ * dK/dV are [B,Sk,Hkv,D]: fp32 contiguous when dkv_fp32 != 0 (the ring's travelling
+ * partial sums), else element type `dtype` with the strides dkv_sb/ss/sh (all zero =
+ * contiguous). With dkv_accumulate != 0 the block result is added to what dk/dv
+ * already hold (sp_aurora/ring_flash_attn.py:139-141), otherwise it overwrites them.
+ * deterministic != 0 restricts the launcher to paths whose floating-point summation
+ * order does not depend on scheduling (results are then bitwise reproducible).
+ * The backward runs as two kernels, a K/V-stationary pass (dK, dV) and a
+ * query-stationary pass (dQ). passes selects them: SPA_BWD_BOTH, SPA_BWD_DQ_ONLY (dk, dv
+ * may be NULL) or SPA_BWD_DKV_ONLY (dq, dq_acc may be NULL), so that a ring step can
+ * run its dQ pass while the travelling dK|dV partial is still in flight.
  */
+#define SPA_BWD_BOTH 0
+#define SPA_BWD_DQ_ONLY 1
+#define SPA_BWD_DKV_ONLY 2
+
 typedef struct spa_bwd_args {
   const void* q;    int64_t q_sb, q_ss, q_sh;
   const void* k;    int64_t k_sb, k_ss, k_sh;
   const void* v;    int64_t v_sb, v_ss, v_sh;
   const void* dout; int64_t do_sb, do_ss, do_sh;
-  const float* lse;      /* [B,Hq,Sq] */
-  const float* delta;    /* [B,Hq,Sq] */
-  float* dq_acc;         /* [B,Sq,Hq,D] fp32 contiguous, accumulated */
-  void* dk;              /* [B,Sk,Hkv,D] contiguous */
+  const float* lse;      /* [B,Hq,Sq], strides lse_sb / lse_sh */
+  const float* delta;    /* same layout as lse */
+  int64_t lse_sb, lse_sh;
+  float* dq_acc;         /* [B,Sq,Hq,D] fp32 contiguous, may be NULL (see above) */
+  void* dq;              /* [B,Sq,Hq,D] element type `dtype`, may be NULL */
+  int64_t dq_sb, dq_ss, dq_sh;
+  int32_t dq_overwrite;
+  void* dk;              /* [B,Sk,Hkv,D] */
   void* dv;
+  int64_t dkv_sb, dkv_ss, dkv_sh;
   int32_t dkv_fp32;
   int32_t dkv_accumulate;
+  int32_t deterministic;
+  int32_t passes;
   int32_t B, Sq, Sk, Hq, Hkv, D;
   int32_t dtype;
   int32_t causal;
@@ -127,23 +152,26 @@ int spa_attn_bwd(const spa_bwd_args* args);
  * No counterpart in the reference. Who needs it: code that runs where every
  * byte of the GPU already belongs to someone else's pool, or that may not call
  * into the CUDA allocator at all (a fixed-budget service, a thread that must
- * not block on allocator locks). spa_attn_bwd makes such a caller bring two
- * scratch buffers (delta and the fp32 dq accumulator); this entry keeps them in
- * a fixed array inside the library instead. The caller passes only inputs
+ * not block on allocator locks). spa_attn_bwd makes such a caller bring a
+ * scratch buffer (delta, the row sums of dO * O); this entry keeps it in a fixed
+ * array inside the library instead. The caller passes only inputs
  * (q, k, v, out, dout, lse) and outputs (dq, dk, dv: element type `dtype`,
  * contiguous [B,Sq,Hq,D] / [B,Sk,Hkv,D], overwritten).
  *
  * - It calls no cudaMalloc/cudaFree and no allocating library routine.
- * - Limit: B*Sq*Hq*(D+1)*4 bytes (rounded up to 256) must fit in
- *   SPA_NOALLOC_SCRATCH_BYTES; larger problems are rejected with SPA_EINVAL.
- *   Every GPU that loads the library holds that array until the process exits.
+ * - Limit: B*Sq*Hq*4 bytes must fit in SPA_NOALLOC_SCRATCH_BYTES; larger problems
+ *   are rejected with SPA_EINVAL. Every GPU that loads the library holds that
+ *   array until the process exits.
  * - The first call on a device looks up the array's device address; make that
  *   first call before starting any stream capture.
- * - All calls share the one array (it is re-zeroed at the start of each call):
+ * - All calls share the one array, which keeps the last call's contents. Nothing in
+ *   it has to start at zero (each call writes every delta value it later reads), but
  *   calls that overlap on the same GPU, e.g. from two streams, race. Serialise them.
- * - The arithmetic runs on the fp32 CUDA-core kernels for every dtype.
+ * - bf16/fp16 with head_dim 64 or 128 run on the tensor-core kernels, everything
+ *   else on the fp32 CUDA-core kernels, as in spa_attn_bwd; results are bitwise
+ *   reproducible.
  */
-#define SPA_NOALLOC_SCRATCH_BYTES (64u << 20)
+#define SPA_NOALLOC_SCRATCH_BYTES (16u << 20)
 
 typedef struct spa_bwd_noalloc_args {
   const void* q;    int64_t q_sb, q_ss, q_sh;

@@ -31,7 +31,9 @@ from .all_to_all import (  # noqa: F401
 from .ulysses import (  # noqa: F401
     AttnType,
     UlyssesAttention,
+    UlyssesComm,
     UlyssesFlashAttnFunc,
+    select_flash_attn_impl,
     ulysses_flash_attn_func,
     ulysses_flash_attn_kvpacked_func,
     ulysses_flash_attn_qkvpacked_func,
@@ -49,8 +51,22 @@ sp_aurora_func = ring_flash_attn_func
 sp_aurora_kvpacked_func = ring_flash_attn_kvpacked_func
 sp_aurora_qkvpacked_func = ring_flash_attn_qkvpacked_func
 
+# The reference's own spellings (sp_aurora/intel_ring_flash_attn.py:453-456,
+# sp_aurora/intel_ulysses_attn.py:501-624, sp_aurora/__init__.py:59-72).
+intel_ring_flash_attn_func = ring_flash_attn_func
+intel_ring_flash_attn_kvpacked_func = ring_flash_attn_kvpacked_func
+intel_ring_flash_attn_qkvpacked_func = ring_flash_attn_qkvpacked_func
+IntelRingFlashAttnFunc = RingFlashAttnFunc
+intel_ulysses_flash_attn_func = ulysses_flash_attn_func
+intel_ulysses_flash_attn_kvpacked_func = ulysses_flash_attn_kvpacked_func
+intel_ulysses_flash_attn_qkvpacked_func = ulysses_flash_attn_qkvpacked_func
+IntelUlyssesComm = UlyssesComm
+IntelSeqAllToAll4D = SeqAllToAll4D
+
+# Feature flags of sp_aurora/globals.py:171-173.
 HAS_LONG_CTX_ATTN = True
 HAS_FLASH_ATTN = True
+HAS_SPARSE_SAGE_ATTENTION = False
 
 
 def is_available() -> bool:

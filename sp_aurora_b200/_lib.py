@@ -17,6 +17,7 @@ _LIB_PATH = Path(os.environ.get("SPA_LIB_PATH") or
                  Path(__file__).resolve().parent / "libspaurora_sm100.so")
 
 SPA_OK = 0
+SPA_BWD_BOTH, SPA_BWD_DQ_ONLY, SPA_BWD_DKV_ONLY = 0, 1, 2
 DTYPE_CODE = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
 
 
@@ -31,7 +32,7 @@ class FwdArgs(C.Structure):
         ("v", C.c_void_p), ("v_sb", C.c_int64), ("v_ss", C.c_int64), ("v_sh", C.c_int64),
         ("out", C.c_void_p), ("o_sb", C.c_int64), ("o_ss", C.c_int64), ("o_sh", C.c_int64),
         ("out_acc", C.c_void_p),
-        ("lse", C.c_void_p),
+        ("lse", C.c_void_p), ("lse_sb", C.c_int64), ("lse_sh", C.c_int64),
         ("B", C.c_int32), ("Sq", C.c_int32), ("Sk", C.c_int32),
         ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32),
         ("dtype", C.c_int32), ("causal", C.c_int32), ("causal_off", C.c_int32),
@@ -47,9 +48,14 @@ class BwdArgs(C.Structure):
         ("k", C.c_void_p), ("k_sb", C.c_int64), ("k_ss", C.c_int64), ("k_sh", C.c_int64),
         ("v", C.c_void_p), ("v_sb", C.c_int64), ("v_ss", C.c_int64), ("v_sh", C.c_int64),
         ("dout", C.c_void_p), ("do_sb", C.c_int64), ("do_ss", C.c_int64), ("do_sh", C.c_int64),
-        ("lse", C.c_void_p), ("delta", C.c_void_p), ("dq_acc", C.c_void_p),
+        ("lse", C.c_void_p), ("delta", C.c_void_p), ("lse_sb", C.c_int64), ("lse_sh", C.c_int64),
+        ("dq_acc", C.c_void_p),
+        ("dq", C.c_void_p), ("dq_sb", C.c_int64), ("dq_ss", C.c_int64), ("dq_sh", C.c_int64),
+        ("dq_overwrite", C.c_int32),
         ("dk", C.c_void_p), ("dv", C.c_void_p),
-        ("dkv_fp32", C.c_int32), ("dkv_accumulate", C.c_int32),
+        ("dkv_sb", C.c_int64), ("dkv_ss", C.c_int64), ("dkv_sh", C.c_int64),
+        ("dkv_fp32", C.c_int32), ("dkv_accumulate", C.c_int32), ("deterministic", C.c_int32),
+        ("passes", C.c_int32),
         ("B", C.c_int32), ("Sq", C.c_int32), ("Sk", C.c_int32),
         ("Hq", C.c_int32), ("Hkv", C.c_int32), ("D", C.c_int32),
         ("dtype", C.c_int32), ("causal", C.c_int32), ("causal_off", C.c_int32),

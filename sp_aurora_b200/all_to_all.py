@@ -22,7 +22,8 @@ from . import _lib
 from ._lib import check, lib
 
 __all__ = ["all_to_all_4D", "all_to_all_5D", "SeqAllToAll4D", "SeqAllToAll5D",
-           "seq_all_to_all_4d_inference", "strided_copy"]
+           "seq_all_to_all_4d_inference", "strided_copy", "heads_all_to_all_packed",
+           "seq_all_to_all_packed"]
 
 
 def _coalesce(shape, sst, dst):
@@ -162,6 +163,83 @@ def all_to_all_5D(input: torch.Tensor, scatter_idx: int = 3, gather_idx: int = 1
     if use_sync and out.is_cuda:
         torch.cuda.current_stream(out.device).synchronize()
     return out
+
+
+def heads_all_to_all_packed(tensors, group=None, copy_fn: Callable = strided_copy):
+    """Sequence -> head reshard of several [B, S/P, H_i, D] tensors (q, k, v with their
+    own head counts) as ONE all-to-all message instead of one per tensor
+    (sp_aurora/intel_ulysses_attn.py:156-170 sends q, k and v separately).
+
+    The message is laid out (P, B, S/P, sum_i H_i/P, D): every token row carries its q
+    heads, then its k heads, then its v heads. Returns [B, S, H_i/P, D] views of the
+    gathered buffer (last dimension contiguous, row stride sum_i H_i/P * D), which the
+    attention kernels read in place."""
+    P = _world(group)
+    if P == 1:
+        return list(tensors)
+    B, Sl, _, D = tensors[0].shape
+    hs = []
+    for t in tensors:
+        if t.dim() != 4 or t.shape[0] != B or t.shape[1] != Sl or t.shape[3] != D:
+            raise ValueError("packed all-to-all needs [B, S_local, H_i, D] tensors of one B, S_local, D")
+        if t.shape[2] % P:
+            raise ValueError(f"number of heads ({t.shape[2]}) must be divisible by the group size ({P})")
+        hs.append(t.shape[2] // P)
+    hsum = sum(hs)
+    send = torch.empty((P, B, Sl, hsum, D), dtype=tensors[0].dtype, device=tensors[0].device)
+    o = 0
+    for t, h in zip(tensors, hs):
+        copy_fn(send[:, :, :, o:o + h], t.unflatten(2, (P, h)).permute(2, 0, 1, 3, 4))
+        o += h
+    recv = _exchange(send, group)                           # [P_src, B, Sl, hsum, D]
+    if B == 1:
+        full = recv.view(1, P * Sl, hsum, D)
+    else:
+        full = torch.empty((B, P * Sl, hsum, D), dtype=recv.dtype, device=recv.device)
+        copy_fn(full.view(B, P, Sl, hsum, D), recv.permute(1, 0, 2, 3, 4))
+    outs, o = [], 0
+    for h in hs:
+        outs.append(full[:, :, o:o + h])
+        o += h
+    return outs
+
+
+def seq_all_to_all_packed(tensors, group=None, copy_fn: Callable = strided_copy):
+    """Head -> sequence reshard of several [B, S, H_i/P, D] tensors (dq, dk, dv) as ONE
+    message; the inverse of heads_all_to_all_packed. Tensors that are adjacent head
+    slices of one [1, S, sum h_i, D] buffer are sent from where they lie."""
+    P = _world(group)
+    if P == 1:
+        return list(tensors)
+    B, S, _, D = tensors[0].shape
+    if S % P:
+        raise ValueError(f"sequence length ({S}) must be divisible by the group size ({P})")
+    Sl = S // P
+    hs = [t.shape[2] for t in tensors]
+    hsum = sum(hs)
+    t0 = tensors[0]
+    in_place = B == 1 and t0.stride() == (S * hsum * D, hsum * D, D, 1)
+    o = 0
+    for t, h in zip(tensors, hs):
+        in_place = in_place and t.stride() == t0.stride() and \
+            t.data_ptr() == t0.data_ptr() + o * D * t0.element_size()
+        o += h
+    if in_place:
+        send = torch.as_strided(t0, (P, 1, Sl, hsum, D), (Sl * hsum * D, Sl * hsum * D, hsum * D, D, 1))
+    else:
+        send = torch.empty((P, B, Sl, hsum, D), dtype=t0.dtype, device=t0.device)
+        o = 0
+        for t, h in zip(tensors, hs):
+            copy_fn(send[:, :, :, o:o + h], t.unflatten(1, (P, Sl)).permute(1, 0, 2, 3, 4))
+            o += h
+    recv = _exchange(send, group)                           # [P_src (head group), B, Sl, hsum, D]
+    outs, o = [], 0
+    for h in hs:
+        out = torch.empty((B, Sl, P * h, D), dtype=t0.dtype, device=t0.device)
+        copy_fn(out.view(B, Sl, P, h, D), recv[:, :, :, o:o + h].permute(1, 2, 0, 3, 4))
+        outs.append(out)
+        o += h
+    return outs
 
 
 class SeqAllToAll4D(torch.autograd.Function):

@@ -20,8 +20,8 @@ from pathlib import Path
 PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libspaurora_sm100.so"
-SOURCES = ["spa_abi.cu", "attn_fwd_sm100.cu", "attn_bwd_sm100.cu", "attn_bwd_f32out_sm100.cu",
-           "attn_bwd128_sm100.cu", "attn_simt.cu"]
+SOURCES = ["spa_abi.cu", "attn_fwd_sm100.cu", "attn_bwd_dq_sm100.cu", "attn_bwd_dkv_sm100.cu",
+           "attn_simt.cu"]
 HEADERS = [CSRC / "tc05.cuh", CSRC / "spa_internal.h", PKG_DIR.parent / "include" / "spa.h"]
 
 NVCC_FLAGS = [

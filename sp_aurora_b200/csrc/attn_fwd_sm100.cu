@@ -34,6 +34,14 @@ constexpr int kTileM = 128;          // query rows per tile
 constexpr int kTileN = 128;          // keys per K/V tile
 constexpr int kThreads = 320;
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
+// The 128x128 exponentials of a key tile would keep the special-function unit busy for as
+// long as the tile's MMAs take. One column pair in every kPolyPeriod pairs is therefore
+// evaluated on the FMA pipe (poly_exp2, relative error 7.5e-5, far below the rounding of
+// P to 16 bits); 0 sends everything to ex2.approx.
+#ifndef SPA_FWD_POLY_PERIOD
+#define SPA_FWD_POLY_PERIOD 4
+#endif
+constexpr int kPolyPeriod = SPA_FWD_POLY_PERIOD;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -47,8 +55,8 @@ struct FwdParams {
   int64_t o_sb, o_ss, o_sh;
   float* out_acc;
   float* lse;
+  int64_t lse_sb, lse_sh;
   int* status;
-  unsigned long long* prof;  // optional global array [32] of blocked cycles per wait site
 };
 
 template <int D>
@@ -60,8 +68,7 @@ struct FwdSmem {
   static constexpr int kKVOff = kQOff + 2 * kTileBytes;
   static constexpr int kBarOff = kKVOff + kStages * kTileBytes;
   static constexpr int kNumBars = 1 + 2 * kStages + 6;
-  static constexpr int kProfOff = kBarOff + kNumBars * 8 + 16;   // 32 x u64 wait profile
-  static constexpr int kTotal = kProfOff + 32 * 8;
+  static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
 };
 
 template <typename T>
@@ -135,7 +142,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   }
   const int nmax = max(n_t[0], n_t[1]);
 
-  if (threadIdx.x < 32) reinterpret_cast<unsigned long long*>(smem + L::kProfOff)[threadIdx.x] = 0;
   if (threadIdx.x == 0) {
     *cta_abort = 0;
     mbar_init(q_full, 1);
@@ -159,9 +165,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  unsigned long long* prof_s = reinterpret_cast<unsigned long long*>(smem + L::kProfOff);
-  WaitCtx wc{p.status, cta_abort, p.prof ? prof_s : nullptr};
-  const long long t_start = clock64();
+  WaitCtx wc{p.status, cta_abort};
 
   if (warp == 8) {
     // ------------------------------------------------------------------ TMA
@@ -321,8 +325,11 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       float lsum = 0.f;
 #pragma unroll
       for (int c = 0; c < 128; c += 2) {
-        const float p0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_eff));
-        const float p1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_eff));
+        const float x0 = fmaf(s[c], p.scale_log2, -m_eff);
+        const float x1 = fmaf(s[c + 1], p.scale_log2, -m_eff);
+        const bool poly = kPolyPeriod > 0 && ((c >> 1) % (kPolyPeriod > 0 ? kPolyPeriod : 1)) == 0;
+        const float p0 = poly ? poly_exp2(x0) : fast_exp2(x0);
+        const float p1 = poly ? poly_exp2(x1) : fast_exp2(x1);
         lsum += p0 + p1;
         pk[c >> 1] = pack2<T>(p0, p1);
       }
@@ -365,7 +372,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       const bool have = (nt > 0) && (l > 0.f);
       const float inv_l = have ? 1.f / l : 0.f;
       const float lse_blk = have ? (m_used + log2f(l)) * kLn2 : ninf;
-      const size_t lse_idx = ((size_t)b * p.Hq + h) * p.Sq + qrow;
+      const size_t lse_idx = (size_t)b * p.lse_sb + (size_t)h * p.lse_sh + qrow;
       float w_old = 0.f, w_blk = have ? 1.f : 0.f, lse_new = lse_blk;
       if (p.merge_prev && row_ok) {
         const float lse_old = p.lse[lse_idx];
@@ -440,11 +447,6 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     for (int i = 0; i < 64; ++i) __nanosleep(2000);
     __syncthreads();
   }
-  if (p.prof && threadIdx.x < 32) {
-    if (threadIdx.x == 31) prof_s[31] = (unsigned long long)(clock64() - t_start);  // CTA lifetime
-    __syncwarp();
-    atomicAdd(&p.prof[threadIdx.x], prof_s[threadIdx.x]);
-  }
   if (warp == 9) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
@@ -468,21 +470,13 @@ int launch_fwd_typed(const spa_fwd_args* a, int is_bf16) {
   p.chunk = (!a->causal || p.n_qblk >= 256) ? p.n_qblk : 1;
   p.scale_log2 = a->scale * kLog2e;
   p.out = a->out; p.o_sb = a->o_sb; p.o_ss = a->o_ss; p.o_sh = a->o_sh;
-  p.out_acc = a->out_acc; p.lse = a->lse;
+  p.out_acc = a->out_acc; p.lse = a->lse; p.lse_sb = a->lse_sb; p.lse_sh = a->lse_sh;
   p.status = device_status_word();
   if (!p.status) return SPA_ECUDA;
-  p.prof = wait_profile_buffer();   // nullptr unless SPA_WAIT_PROFILE=1
   const int smem_bytes = L::kTotal + 1024;
   auto kern = attn_fwd_sm100_kernel<D, T>;
-  static bool attr_set = false;  // per instantiation
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-    if (e != cudaSuccess) {
-      set_error("cudaFuncSetAttribute(fwd sm100): %s", cudaGetErrorString(e));
-      return SPA_ECUDA;
-    }
-    attr_set = true;
-  }
+  int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem_bytes, "fwd sm100");
+  if (rc) return rc;
   const long long grid = (long long)p.n_qblk * a->B * a->Hq;
   if (grid <= 0 || grid > 0x7fffffffll) {
     set_error("fwd grid out of range");
@@ -494,7 +488,6 @@ int launch_fwd_typed(const spa_fwd_args* a, int is_bf16) {
     set_error("fwd sm100 launch: %s", cudaGetErrorString(e));
     return SPA_ECUDA;
   }
-  if (p.prof) wait_profile_report("fwd", (cudaStream_t)a->stream);
   return SPA_OK;
 }
 

@@ -94,6 +94,7 @@ struct SimtFwdParams {
   int64_t o_sb, o_ss, o_sh;
   float* out_acc;
   float* lse;
+  int64_t lse_sb, lse_sh;
   int B, Sq, Sk, Hq, Hkv, causal, causal_off, merge_prev;
   float scale;
 };
@@ -190,7 +191,7 @@ attn_fwd_simt_kernel(const SimtFwdParams p) {
   const bool have = l > 0.f;
   const float inv_l = have ? 1.f / l : 0.f;
   const float lse_blk = have ? m + logf(l) : -INFINITY;
-  const size_t lse_idx = ((size_t)b * p.Hq + h) * p.Sq + row;
+  const size_t lse_idx = (size_t)b * p.lse_sb + (size_t)h * p.lse_sh + row;
   float w_old = 0.f, w_blk = have ? 1.f : 0.f, lse_new = lse_blk;
   if (p.merge_prev) {
     const float lse_old = p.lse[lse_idx];
@@ -233,9 +234,14 @@ struct SimtBwdParams {
   int64_t q_sb, q_ss, q_sh, k_sb, k_ss, k_sh, v_sb, v_ss, v_sh, do_sb, do_ss, do_sh;
   const float* lse;
   const float* delta;
+  int64_t lse_sb, lse_sh;
   float* dq_acc;
+  void* dq;
+  int64_t dq_sb, dq_ss, dq_sh;
+  int dq_overwrite;
   void* dk;
   void* dv;
+  int64_t dkv_sb, dkv_ss, dkv_sh;
   int dkv_fp32, dkv_accumulate;
   int B, Sq, Sk, Hq, Hkv, causal, causal_off;
   float scale;
@@ -266,7 +272,7 @@ attn_bwd_dq_simt_kernel(const SimtBwdParams p) {
     dov[i] = load4<T>(dop + 4 * (4 * i + sl));
     dq[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
-  const size_t sidx = ((size_t)b * p.Hq + h) * p.Sq + rowc;
+  const size_t sidx = (size_t)b * p.lse_sb + (size_t)h * p.lse_sh + rowc;
   const float lse = p.lse[sidx];
   const float delta = p.delta[sidx];
 
@@ -316,16 +322,22 @@ attn_bwd_dq_simt_kernel(const SimtBwdParams p) {
     }
   }
   if (!row_ok) return;
-  float* dst = p.dq_acc + (((size_t)b * p.Sq + row) * p.Hq + h) * D;
+  // total = (earlier ring steps' sum, unless this is the first) + this block; it goes to
+  // dq in the element type and / or back to the fp32 accumulator, whichever is given.
+  float* acc = p.dq_acc ? p.dq_acc + (((size_t)b * p.Sq + row) * p.Hq + h) * D : nullptr;
+  T* dst = p.dq ? reinterpret_cast<T*>(p.dq) + b * p.dq_sb + (int64_t)row * p.dq_ss + h * p.dq_sh
+                : nullptr;
 #pragma unroll
   for (int i = 0; i < NF; ++i) {
     const int e = 4 * (4 * i + sl);
-    float4 a = *reinterpret_cast<float4*>(dst + e);
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (!p.dq_overwrite) a = *reinterpret_cast<const float4*>(acc + e);
     a.x = fmaf(p.scale, dq[i].x, a.x);
     a.y = fmaf(p.scale, dq[i].y, a.y);
     a.z = fmaf(p.scale, dq[i].z, a.z);
     a.w = fmaf(p.scale, dq[i].w, a.w);
-    *reinterpret_cast<float4*>(dst + e) = a;
+    if (dst) store4<T>(dst + e, a);
+    if (acc) *reinterpret_cast<float4*>(acc + e) = a;
   }
 }
 
@@ -365,7 +377,7 @@ attn_bwd_dkv_simt_kernel(const SimtBwdParams p) {
     const int h = g * G + hh;
     const T* qbase = reinterpret_cast<const T*>(p.q) + b * p.q_sb + h * p.q_sh;
     const T* dobase = reinterpret_cast<const T*>(p.dout) + b * p.do_sb + h * p.do_sh;
-    const size_t sbase = ((size_t)b * p.Hq + h) * p.Sq;
+    const size_t sbase = (size_t)b * p.lse_sb + (size_t)h * p.lse_sh;
     for (int q0 = q_begin; q0 < p.Sq; q0 += kTile) {
       __syncthreads();
       const int nv = min(kTile, p.Sq - q0);
@@ -410,7 +422,8 @@ attn_bwd_dkv_simt_kernel(const SimtBwdParams p) {
     }
   }
   if (!row_ok) return;
-  const size_t off = (((size_t)b * p.Sk + krow) * p.Hkv + g) * D;
+  const size_t off = (((size_t)b * p.Sk + krow) * p.Hkv + g) * D;                   // fp32: contiguous
+  const int64_t off_t = b * p.dkv_sb + (int64_t)krow * p.dkv_ss + g * p.dkv_sh;     // element type: strided
 #pragma unroll
   for (int i = 0; i < NF; ++i) {
     const int e = 4 * (4 * i + sl);
@@ -427,8 +440,8 @@ attn_bwd_dkv_simt_kernel(const SimtBwdParams p) {
       *reinterpret_cast<float4*>(pk) = a;
       *reinterpret_cast<float4*>(pv) = c;
     } else {
-      T* pk = reinterpret_cast<T*>(p.dk) + off + e;
-      T* pv = reinterpret_cast<T*>(p.dv) + off + e;
+      T* pk = reinterpret_cast<T*>(p.dk) + off_t + e;
+      T* pv = reinterpret_cast<T*>(p.dv) + off_t + e;
       if (p.dkv_accumulate) {
         const float4 x = load4<T>(pk), y = load4<T>(pv);
         a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
@@ -449,6 +462,7 @@ int launch_fwd_simt_typed(const spa_fwd_args* a) {
   p.v_sb = a->v_sb; p.v_ss = a->v_ss; p.v_sh = a->v_sh;
   p.out = a->out; p.o_sb = a->o_sb; p.o_ss = a->o_ss; p.o_sh = a->o_sh;
   p.out_acc = a->out_acc; p.lse = a->lse;
+  p.lse_sb = a->lse_sb; p.lse_sh = a->lse_sh;
   p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.Hq = a->Hq; p.Hkv = a->Hkv;
   p.causal = a->causal; p.causal_off = a->causal_off; p.merge_prev = a->merge_prev;
   p.scale = a->scale;
@@ -470,15 +484,18 @@ int launch_bwd_simt_typed(const spa_bwd_args* a) {
   p.k_sb = a->k_sb; p.k_ss = a->k_ss; p.k_sh = a->k_sh;
   p.v_sb = a->v_sb; p.v_ss = a->v_ss; p.v_sh = a->v_sh;
   p.do_sb = a->do_sb; p.do_ss = a->do_ss; p.do_sh = a->do_sh;
-  p.lse = a->lse; p.delta = a->delta; p.dq_acc = a->dq_acc; p.dk = a->dk; p.dv = a->dv;
+  p.lse = a->lse; p.delta = a->delta; p.lse_sb = a->lse_sb; p.lse_sh = a->lse_sh;
+  p.dq_acc = a->dq_acc; p.dq = a->dq; p.dq_sb = a->dq_sb; p.dq_ss = a->dq_ss; p.dq_sh = a->dq_sh;
+  p.dq_overwrite = a->dq_overwrite;
+  p.dk = a->dk; p.dv = a->dv; p.dkv_sb = a->dkv_sb; p.dkv_ss = a->dkv_ss; p.dkv_sh = a->dkv_sh;
   p.dkv_fp32 = a->dkv_fp32; p.dkv_accumulate = a->dkv_accumulate;
   p.B = a->B; p.Sq = a->Sq; p.Sk = a->Sk; p.Hq = a->Hq; p.Hkv = a->Hkv;
   p.causal = a->causal; p.causal_off = a->causal_off; p.scale = a->scale;
   cudaStream_t st = (cudaStream_t)a->stream;
   dim3 gq(ceil_div(a->Sq, kRows), a->Hq, a->B);
-  attn_bwd_dq_simt_kernel<D, T><<<gq, kThreadsSimt, 0, st>>>(p);
+  if (a->passes != SPA_BWD_DKV_ONLY) attn_bwd_dq_simt_kernel<D, T><<<gq, kThreadsSimt, 0, st>>>(p);
   dim3 gk(ceil_div(a->Sk, kRows), a->Hkv, a->B);
-  attn_bwd_dkv_simt_kernel<D, T><<<gk, kThreadsSimt, 0, st>>>(p);
+  if (a->passes != SPA_BWD_DQ_ONLY) attn_bwd_dkv_simt_kernel<D, T><<<gk, kThreadsSimt, 0, st>>>(p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     set_error("bwd simt launch: %s", cudaGetErrorString(e));

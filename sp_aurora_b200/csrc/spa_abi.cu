@@ -30,6 +30,9 @@ static std::atomic<long long> g_launches{0};
 static inline void note_launch(int n = 1) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 // --------------------------------------------------------- device status word
+// Four ints per device, part of the library image (zero until a bounded wait gives up);
+// host code needs the device address, looked up once per device.
+static __device__ int g_status_dev[4];
 static std::mutex g_status_mu;
 static int* g_status[64] = {nullptr};
 
@@ -41,50 +44,67 @@ int* device_status_word() {
   }
   std::lock_guard<std::mutex> lk(g_status_mu);
   if (!g_status[dev]) {
-    int* p = nullptr;
-    cudaError_t e = cudaMalloc(&p, 4 * sizeof(int));
-    if (e == cudaSuccess) e = cudaMemset(p, 0, 4 * sizeof(int));
-    if (e != cudaSuccess) {
-      set_error("status word allocation: %s", cudaGetErrorString(e));
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_status_dev);
+    if (e != cudaSuccess || !p) {
+      set_error("status word lookup: %s", cudaGetErrorString(e));
       return nullptr;
     }
-    g_status[dev] = p;
+    g_status[dev] = static_cast<int*>(p);
   }
   return g_status[dev];
 }
 
-// ------------------------------------------------------------ wait profile
-static unsigned long long* g_prof = nullptr;
-unsigned long long* wait_profile_buffer() {
-  static int on = -1;
-  if (on < 0) {
-    const char* e = getenv("SPA_WAIT_PROFILE");
-    on = (e && e[0] == '1') ? 1 : 0;
-  }
-  if (!on) return nullptr;
-  if (!g_prof && cudaMalloc(&g_prof, 160 * sizeof(unsigned long long)) != cudaSuccess) return nullptr;
-  cudaMemset(g_prof, 0, 160 * sizeof(unsigned long long));
-  return g_prof;
-}
-void wait_profile_report(const char* tag, cudaStream_t stream) {
-  unsigned long long h[160];
-  cudaStreamSynchronize(stream);
-  if (cudaMemcpy(h, g_prof, sizeof(h), cudaMemcpyDeviceToHost) != cudaSuccess) return;
-  fprintf(stderr, "[spa wait profile %s] cta_cycles_sum=%llu", tag, h[31]);
-  for (int i = 0; i < 31; ++i)
-    if (h[i]) fprintf(stderr, " s%d=%.3f", i, (double)h[i] / (double)(h[31] ? h[31] : 1));
-  fprintf(stderr, "\n");
-  if (h[32]) {   // timeline of block 0 (events x 8 iterations), relative to the first stamp
-    unsigned long long t0 = ~0ull;
-    for (int i = 32; i < 160; ++i)
-      if (h[i] && h[i] < t0) t0 = h[i];
-    for (int ev = 0; ev < 16; ++ev) {
-      if (!h[32 + ev * 8]) continue;
-      fprintf(stderr, "  ev%-2d", ev);
-      for (int i = 0; i < 8; ++i) fprintf(stderr, " %7lld", (long long)(h[32 + ev * 8 + i] - t0));
-      fprintf(stderr, "\n");
+// --------------------------------------------- per-device kernel attributes
+namespace {
+struct SmemAttrEntry {
+  const void* kernel;
+  int device;
+  int bytes;
+};
+std::mutex g_attr_mu;
+SmemAttrEntry g_attr[256];
+int g_attr_n = 0;
+}  // namespace
+
+// Pure bookkeeping of ensure_dynamic_smem: true when (kernel, device) was already raised
+// to at least `bytes`; otherwise records it and returns false.
+bool smem_attr_seen(const void* kernel, int device, int bytes) {
+  std::lock_guard<std::mutex> lk(g_attr_mu);
+  for (int i = 0; i < g_attr_n; ++i)
+    if (g_attr[i].kernel == kernel && g_attr[i].device == device) {
+      if (g_attr[i].bytes >= bytes) return true;
+      g_attr[i].bytes = bytes;
+      return false;
     }
+  if (g_attr_n < 256) g_attr[g_attr_n++] = SmemAttrEntry{kernel, device, bytes};
+  return false;
+}
+
+int ensure_dynamic_smem(const void* kernel, int bytes, const char* what) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    set_error("cudaGetDevice failed");
+    return SPA_ECUDA;
   }
+  if (smem_attr_seen(kernel, dev, bytes)) return SPA_OK;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  if (e != cudaSuccess) {
+    set_error("cudaFuncSetAttribute(%s, %d bytes): %s", what, bytes, cudaGetErrorString(e));
+    return SPA_ECUDA;
+  }
+  return SPA_OK;
+}
+
+int device_sm_count() {
+  static std::atomic<int> cache[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int v = cache[dev].load(std::memory_order_relaxed);
+  if (v > 0) return v;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+  cache[dev].store(v, std::memory_order_relaxed);
+  return v;
 }
 
 // ------------------------------------------------------- TMA descriptor encode
@@ -519,11 +539,19 @@ static int validate_common(int B, int Sq, int Sk, int Hq, int Hkv, int D, int dt
   return SPA_OK;
 }
 
-int spa_attn_fwd(const spa_fwd_args* a) {
-  if (!a || !a->q || !a->k || !a->v || !a->lse) {
+static bool misaligned(const void* p, int64_t sb, int64_t ss, int64_t sh, int elt, int vec_bytes) {
+  return ((uintptr_t)p % vec_bytes) || ((sb * elt) % vec_bytes) || ((ss * elt) % vec_bytes) ||
+         ((sh * elt) % vec_bytes);
+}
+static int elt_size(int dtype) { return dtype == SPA_DTYPE_F32 ? 4 : 2; }
+
+int spa_attn_fwd(const spa_fwd_args* args) {
+  if (!args || !args->q || !args->k || !args->v || !args->lse) {
     set_error("spa_attn_fwd: null pointer argument");
     return SPA_EINVAL;
   }
+  spa_fwd_args n = *args;
+  const spa_fwd_args* a = &n;
   int rc = validate_common(a->B, a->Sq, a->Sk, a->Hq, a->Hkv, a->D, a->dtype, a->scale);
   if (rc) return rc;
   if (!a->out && !a->out_acc) {
@@ -534,34 +562,111 @@ int spa_attn_fwd(const spa_fwd_args* a) {
     set_error("spa_attn_fwd: merge_prev needs out_acc");
     return SPA_EINVAL;
   }
+  if (n.lse_sb == 0 && n.lse_sh == 0) {
+    n.lse_sh = a->Sq;
+    n.lse_sb = (int64_t)a->Hq * a->Sq;
+  }
+  // Rows are read and written as 16-byte vectors by every kernel.
+  const int es = elt_size(a->dtype);
+  if (misaligned(a->q, a->q_sb, a->q_ss, a->q_sh, es, 16) ||
+      misaligned(a->k, a->k_sb, a->k_ss, a->k_sh, es, 16) ||
+      misaligned(a->v, a->v_sb, a->v_ss, a->v_sh, es, 16) ||
+      (a->out && misaligned(a->out, a->o_sb, a->o_ss, a->o_sh, es, 16)) ||
+      (a->out_acc && ((uintptr_t)a->out_acc & 15))) {
+    set_error("spa_attn_fwd: tensor bases and strides must be multiples of 16 bytes");
+    return SPA_EINVAL;
+  }
   const bool tensor_core = a->dtype != SPA_DTYPE_F32 && a->D != 32 && !force_simt();
   rc = tensor_core ? launch_fwd_sm100(a) : launch_fwd_simt(a);
   if (rc == SPA_OK) note_launch(1);
   return rc;
 }
 
-int spa_attn_bwd(const spa_bwd_args* a) {
-  if (!a || !a->q || !a->k || !a->v || !a->dout || !a->lse || !a->delta || !a->dq_acc || !a->dk ||
-      !a->dv) {
-    set_error("spa_attn_bwd: null pointer argument");
+// Checks shared by spa_attn_bwd and spa_attn_bwd_noalloc, after the zero stride
+// triples have been replaced by the contiguous ones.
+static int validate_bwd(const spa_bwd_args* a) {
+  if (a->passes != SPA_BWD_BOTH && a->passes != SPA_BWD_DQ_ONLY && a->passes != SPA_BWD_DKV_ONLY) {
+    set_error("spa_attn_bwd: unknown passes value %d", a->passes);
     return SPA_EINVAL;
   }
-  int rc = validate_common(a->B, a->Sq, a->Sk, a->Hq, a->Hkv, a->D, a->dtype, a->scale);
-  if (rc) return rc;
+  const bool want_dq = a->passes != SPA_BWD_DKV_ONLY, want_dkv = a->passes != SPA_BWD_DQ_ONLY;
+  if (want_dq && !a->dq && !a->dq_acc) {
+    set_error("spa_attn_bwd: at least one of dq / dq_acc is required");
+    return SPA_EINVAL;
+  }
+  if (want_dq && !a->dq_overwrite && !a->dq_acc) {
+    set_error("spa_attn_bwd: dq_overwrite == 0 needs dq_acc (the earlier steps' sum)");
+    return SPA_EINVAL;
+  }
+  if (want_dkv && (!a->dk || !a->dv)) {
+    set_error("spa_attn_bwd: null dk / dv");
+    return SPA_EINVAL;
+  }
+  if (want_dkv && a->dkv_fp32 && (a->dkv_ss != (int64_t)a->Hkv * a->D || a->dkv_sh != a->D ||
+                      a->dkv_sb != (int64_t)a->Sk * a->Hkv * a->D)) {
+    set_error("spa_attn_bwd: fp32 dk/dv must be contiguous [B,Sk,Hkv,D]");
+    return SPA_EINVAL;
+  }
+  const int es = elt_size(a->dtype);
+  if (misaligned(a->q, a->q_sb, a->q_ss, a->q_sh, es, 16) ||
+      misaligned(a->k, a->k_sb, a->k_ss, a->k_sh, es, 16) ||
+      misaligned(a->v, a->v_sb, a->v_ss, a->v_sh, es, 16) ||
+      misaligned(a->dout, a->do_sb, a->do_ss, a->do_sh, es, 16) ||
+      (want_dq && a->dq && misaligned(a->dq, a->dq_sb, a->dq_ss, a->dq_sh, es, 16)) ||
+      (want_dq && a->dq_acc && ((uintptr_t)a->dq_acc & 15)) ||
+      (want_dkv && (misaligned(a->dk, a->dkv_sb, a->dkv_ss, a->dkv_sh, a->dkv_fp32 ? 4 : es, 16) ||
+                    misaligned(a->dv, a->dkv_sb, a->dkv_ss, a->dkv_sh, a->dkv_fp32 ? 4 : es, 16)))) {
+    set_error("spa_attn_bwd: tensor bases and strides must be multiples of 16 bytes");
+    return SPA_EINVAL;
+  }
+  return SPA_OK;
+}
+
+static void normalise_bwd(spa_bwd_args* n) {
+  if (n->dtype == SPA_DTYPE_F32) n->dkv_fp32 = 0;   // fp32 is the element type: strided like any other
+  if (n->lse_sb == 0 && n->lse_sh == 0) {
+    n->lse_sh = n->Sq;
+    n->lse_sb = (int64_t)n->Hq * n->Sq;
+  }
+  if (n->dq_sb == 0 && n->dq_ss == 0 && n->dq_sh == 0) {
+    n->dq_sh = n->D;
+    n->dq_ss = (int64_t)n->Hq * n->D;
+    n->dq_sb = (int64_t)n->Sq * n->dq_ss;
+  }
+  if (n->dkv_sb == 0 && n->dkv_ss == 0 && n->dkv_sh == 0) {
+    n->dkv_sh = n->D;
+    n->dkv_ss = (int64_t)n->Hkv * n->D;
+    n->dkv_sb = (int64_t)n->Sk * n->dkv_ss;
+  }
+}
+
+// Both passes of the backward on the stream of `a` (already normalised and validated).
+static int run_bwd(const spa_bwd_args* a) {
   const bool tensor_core = a->dtype != SPA_DTYPE_F32 && a->D != 32 && !force_simt();
+  const bool want_dq = a->passes != SPA_BWD_DKV_ONLY, want_dkv = a->passes != SPA_BWD_DQ_ONLY;
+  int rc = SPA_OK;
   if (tensor_core) {
-    static int wide = -1;   // SPA_BWD128=1 selects the (slower, experimental) 128x128-tile kernel
-    if (wide < 0) {
-      const char* e = getenv("SPA_BWD128");
-      wide = (e && e[0] == '1') ? 1 : 0;
-    }
-    if (a->D == 128 && wide) rc = launch_bwd128_sm100(a);
-    else rc = a->dkv_fp32 ? launch_bwd_f32out_sm100(a) : launch_bwd_sm100(a);
+    if (want_dq) rc = launch_bwd_dq_sm100(a);
+    if (rc == SPA_OK && want_dkv) rc = launch_bwd_dkv_sm100(a);
   } else {
     rc = launch_bwd_simt(a);
   }
-  if (rc == SPA_OK) note_launch(tensor_core ? 1 : 2);
+  if (rc == SPA_OK) note_launch((want_dq ? 1 : 0) + (want_dkv ? 1 : 0));
   return rc;
+}
+
+int spa_attn_bwd(const spa_bwd_args* args) {
+  if (!args || !args->q || !args->k || !args->v || !args->dout || !args->lse || !args->delta) {
+    set_error("spa_attn_bwd: null pointer argument");
+    return SPA_EINVAL;
+  }
+  spa_bwd_args n = *args;
+  int rc = validate_common(n.B, n.Sq, n.Sk, n.Hq, n.Hkv, n.D, n.dtype, n.scale);
+  if (rc) return rc;
+  normalise_bwd(&n);
+  rc = validate_bwd(&n);
+  if (rc) return rc;
+  return run_bwd(&n);
 }
 
 #define SPA_DISPATCH_T(dtype, ...)                                 \
@@ -578,6 +683,13 @@ int spa_bwd_delta(const void* out, int64_t o_sb, int64_t o_ss, int64_t o_sh, con
   if (!out || !dout || !delta || B <= 0 || S <= 0 || H <= 0 || !valid_head_dim(D)) {
     set_error("spa_bwd_delta: bad argument");
     return SPA_EINVAL;
+  }
+  {
+    const int es = elt_size(dtype), vec = 16;   // rows are read as 16-byte vectors
+    if (misaligned(out, o_sb, o_ss, o_sh, es, vec) || misaligned(dout, do_sb, do_ss, do_sh, es, vec)) {
+      set_error("spa_bwd_delta: tensor bases and strides must be multiples of %d bytes", vec);
+      return SPA_EINVAL;
+    }
   }
   const long long threads = (long long)B * S * H * (D / 8);
   const int block = 256;
@@ -602,6 +714,10 @@ int spa_merge(float* out_acc, float* lse, const void* block_out, int64_t bo_sb, 
     set_error("spa_merge: bad argument");
     return SPA_EINVAL;
   }
+  if (((uintptr_t)out_acc & 15) || misaligned(block_out, bo_sb, bo_ss, bo_sh, elt_size(dtype), 4 * elt_size(dtype))) {
+    set_error("spa_merge: out_acc must be 16-byte aligned, block_out base and strides multiples of 4 elements");
+    return SPA_EINVAL;
+  }
   const long long threads = (long long)B * S * H * (D / 4);
   const int block = 256;
   const long long grid = (threads + block - 1) / block;
@@ -622,6 +738,10 @@ int spa_cast_from_f32(const float* src, void* dst, int64_t d_sb, int64_t d_ss, i
                       void* stream) {
   if (!src || !dst || B <= 0 || S <= 0 || H <= 0 || !valid_head_dim(D)) {
     set_error("spa_cast_from_f32: bad argument");
+    return SPA_EINVAL;
+  }
+  if (((uintptr_t)src & 15) || misaligned(dst, d_sb, d_ss, d_sh, elt_size(dtype), 4 * elt_size(dtype))) {
+    set_error("spa_cast_from_f32: src must be 16-byte aligned, dst base and strides multiples of 4 elements");
     return SPA_EINVAL;
   }
   const long long threads = (long long)B * S * H * (D / 4);
@@ -684,10 +804,10 @@ int spa_permute_rows(const void* src, void* dst, const int64_t n[4], const int64
 // Some callers may not allocate device memory at all: code running inside a
 // memory pool that already owns the whole GPU, a service with a fixed memory
 // budget, or a host thread that must not take the allocator's locks. For them
-// the scratch of the backward pass (the fp32 dq accumulator and the delta row
-// sums) lives in the fixed array below instead of in caller-provided buffers.
-// The array is part of the library image: every GPU that loads the library
-// holds SPA_NOALLOC_SCRATCH_BYTES of it until the process exits.
+// the scratch of the backward pass (the delta row sums, rowsum(dO * O)) lives in
+// the fixed array below instead of in a caller-provided buffer. The array is
+// part of the library image: every GPU that loads the library holds
+// SPA_NOALLOC_SCRATCH_BYTES of it until the process exits.
 // ---------------------------------------------------------------------------
 static __device__ __align__(256) unsigned char g_noalloc_scratch[SPA_NOALLOC_SCRATCH_BYTES];
 
@@ -725,26 +845,18 @@ int spa_attn_bwd_noalloc(const spa_bwd_noalloc_args* a) {
   }
   int rc = validate_common(a->B, a->Sq, a->Sk, a->Hq, a->Hkv, a->D, a->dtype, a->scale);
   if (rc) return rc;
-  const size_t rows = (size_t)a->B * a->Sq * a->Hq;
-  const size_t delta_bytes = (rows * sizeof(float) + 255) & ~(size_t)255;
-  const size_t dq_bytes = rows * a->D * sizeof(float);
-  if (delta_bytes + dq_bytes > (size_t)SPA_NOALLOC_SCRATCH_BYTES) {
-    set_error("spa_attn_bwd_noalloc: B*Sq*Hq*(D+1)*4 = %zu bytes of scratch needed, the built-in "
-              "scratch holds %zu; use spa_attn_bwd with caller-provided buffers",
-              delta_bytes + dq_bytes, (size_t)SPA_NOALLOC_SCRATCH_BYTES);
+  const size_t delta_bytes = (size_t)a->B * a->Sq * a->Hq * sizeof(float);
+  if (delta_bytes > (size_t)SPA_NOALLOC_SCRATCH_BYTES) {
+    set_error("spa_attn_bwd_noalloc: B*Sq*Hq*4 = %zu bytes of scratch needed, the built-in "
+              "scratch holds %zu; use spa_attn_bwd with a caller-provided delta buffer",
+              delta_bytes, (size_t)SPA_NOALLOC_SCRATCH_BYTES);
     return SPA_EINVAL;
   }
   unsigned char* base = noalloc_scratch_ptr();
   if (!base) return SPA_ECUDA;
+  // Every element of delta this call reads is written by its own delta kernel first, so
+  // nothing in the shared array has to start at zero.
   float* delta = reinterpret_cast<float*>(base);
-  float* dq_acc = reinterpret_cast<float*>(base + delta_bytes);
-  cudaStream_t st = (cudaStream_t)a->stream;
-  // The array keeps whatever the last call left: the accumulator starts at zero.
-  cudaError_t e = cudaMemsetAsync(dq_acc, 0, dq_bytes, st);
-  if (e != cudaSuccess) {
-    set_error("spa_attn_bwd_noalloc: memset: %s", cudaGetErrorString(e));
-    return SPA_ECUDA;
-  }
   rc = spa_bwd_delta(a->out, a->o_sb, a->o_ss, a->o_sh, a->dout, a->do_sb, a->do_ss, a->do_sh, delta,
                      a->B, a->Sq, a->Hq, a->D, a->dtype, a->stream);
   if (rc) return rc;
@@ -754,19 +866,28 @@ int spa_attn_bwd_noalloc(const spa_bwd_noalloc_args* a) {
   b.k = a->k; b.k_sb = a->k_sb; b.k_ss = a->k_ss; b.k_sh = a->k_sh;
   b.v = a->v; b.v_sb = a->v_sb; b.v_ss = a->v_ss; b.v_sh = a->v_sh;
   b.dout = a->dout; b.do_sb = a->do_sb; b.do_ss = a->do_ss; b.do_sh = a->do_sh;
-  b.lse = a->lse; b.delta = delta; b.dq_acc = dq_acc; b.dk = a->dk; b.dv = a->dv;
-  b.dkv_fp32 = 0; b.dkv_accumulate = 0;
+  b.lse = a->lse; b.delta = delta;
+  // dq is written once, in the element type, by the CTA that owns its rows: no fp32
+  // accumulator is needed. dk/dv likewise (a K/V tile belongs to one CTA).
+  b.dq_acc = nullptr; b.dq = a->dq; b.dq_overwrite = 1;
+  b.dk = a->dk; b.dv = a->dv;
+  b.dkv_fp32 = 0; b.dkv_accumulate = 0; b.deterministic = 1;
   b.B = a->B; b.Sq = a->Sq; b.Sk = a->Sk; b.Hq = a->Hq; b.Hkv = a->Hkv; b.D = a->D;
   b.dtype = a->dtype; b.causal = a->causal; b.causal_off = a->causal_off; b.scale = a->scale;
   b.stream = a->stream;
-  // CUDA-core kernels: they need neither the status word nor any other
-  // allocation; dq rows are owned by one CTA each, dk/dv are written directly.
-  rc = launch_bwd_simt(&b);
+  normalise_bwd(&b);
+  rc = validate_bwd(&b);
   if (rc) return rc;
-  note_launch(2);
-  const int64_t d_ss = (int64_t)a->Hq * a->D, d_sb = (int64_t)a->Sq * d_ss;
-  return spa_cast_from_f32(dq_acc, a->dq, d_sb, d_ss, a->D, a->B, a->Sq, a->Hq, a->D, a->dtype, 1.0f,
-                           a->stream);
+  // The tensor-core kernels (bf16/fp16, head_dim 64/128) and the CUDA-core kernels
+  // (fp32, head_dim 32) both run without any allocation: TMA descriptors travel as
+  // kernel parameters and the status word is part of the library image too.
+  return run_bwd(&b);
+}
+
+// Test hook (not part of include/spa.h): the bookkeeping behind the per-device
+// shared-memory attribute cache, callable without a GPU.
+int spa_internal_smem_attr_seen(const void* kernel, int device, int bytes) {
+  return smem_attr_seen(kernel, device, bytes) ? 1 : 0;
 }
 
 }  // extern "C"

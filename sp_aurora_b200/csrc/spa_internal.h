@@ -31,17 +31,18 @@ int encode_f32_rows_map(CUtensorMap* map, const void* ptr, int D, int64_t S, int
 int encode_f32_slab_map(CUtensorMap* map, const void* ptr, int D, int64_t S, int H, int B,
                         int box_rows);
 
-// Debug aid (library built with -DSPA_PROFILE_WAITS and env SPA_WAIT_PROFILE=1): a zeroed device array of 32 counters that
-// the tensor-core kernels fill with cycles blocked per wait site, and a
-// synchronous dump of it to stderr. Returns nullptr when the aid is off.
-unsigned long long* wait_profile_buffer();
-void wait_profile_report(const char* tag, cudaStream_t stream);
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the current device only:
+// done once per (kernel, device), remembered in a small table. Returns a spa status code.
+int ensure_dynamic_smem(const void* kernel, int bytes, const char* what);
 
-// Launchers (return a spa status code).
+// SM count of the current device (cached per device; 148 if the query fails).
+int device_sm_count();
+
+// Launchers (return a spa status code). Arguments arrive normalised: zero stride
+// triples of spa.h are already replaced by the contiguous strides.
 int launch_fwd_sm100(const spa_fwd_args* a);
-int launch_bwd_sm100(const spa_bwd_args* a);          // dK/dV in the input dtype
-int launch_bwd_f32out_sm100(const spa_bwd_args* a);   // fp32 dK/dV (ring steps)
-int launch_bwd128_sm100(const spa_bwd_args* a);   // head_dim 128, 128x128 tiles
+int launch_bwd_dq_sm100(const spa_bwd_args* a);       // query-stationary pass: dQ
+int launch_bwd_dkv_sm100(const spa_bwd_args* a);      // K/V-stationary pass: dK, dV
 int launch_fwd_simt(const spa_fwd_args* a);
 int launch_bwd_simt(const spa_bwd_args* a);
 

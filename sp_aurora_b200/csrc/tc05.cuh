@@ -56,7 +56,6 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 struct WaitCtx {
   int* status;            // global status word (4 ints)
   volatile int* cta_abort;  // shared-memory flag of this CTA
-  unsigned long long* prof;  // optional shared-memory array [32]: cycles blocked per wait site
 };
 
 #ifndef SPA_WAIT_BUDGET_CYCLES
@@ -69,28 +68,13 @@ struct WaitCtx {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w,
                                           int site, int iter) {
   if (*w.cta_abort) return false;
-#ifndef SPA_PROFILE_WAITS
-  // Fast path without reading the clock (a clock read before every wait costs
-  // ~15% of kernel time; the wait profile is a compile-time debugging option).
+  // Fast path without reading the clock (a clock read before every wait costs ~15 % of
+  // kernel time).
   if (mbar_try_wait(bar, parity)) return true;
-  long long t0 = clock64();
-#else
-  long long t0 = clock64();
-  if (mbar_try_wait(bar, parity)) {   // try_wait may itself suspend the thread for a while
-    if (w.prof && (threadIdx.x & 31) == 0)
-      atomicAdd(&w.prof[site & 31], (unsigned long long)(clock64() - t0));
-    return true;
-  }
-#endif
+  const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) {
-#ifdef SPA_PROFILE_WAITS
-      if (w.prof && (threadIdx.x & 31) == 0)
-        atomicAdd(&w.prof[site & 31], (unsigned long long)(clock64() - t0));
-#endif
-      return true;
-    }
+    if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 0x3ff) == 0) {
       if (*w.cta_abort) return false;
       if (*reinterpret_cast<volatile int*>(w.status) != 0) {
@@ -388,6 +372,20 @@ __device__ __forceinline__ void tmem_st_16x128b_x4(uint32_t taddr, const uint32_
 }
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+// 2^x on the FMA pipe: x = n + r with n the nearest integer and r in [-0.5, 0.5], a
+// degree-3 polynomial for 2^r (fitted for minimal relative error on that interval:
+// 7.5e-5), and n added into the exponent field. x is clamped at -125 so the exponent
+// never wraps; +inf and NaN give garbage, callers mask those lanes afterwards.
+__device__ __forceinline__ float poly_exp2(float x) {
+  x = fmaxf(x, -125.f);
+  const float t = x + 12582912.f;            // 1.5 * 2^23: the low mantissa bits now hold n
+  const float r = x - (t - 12582912.f);
+  float p = fmaf(r, 0.05517125502228737f, 0.2426103800535202f);
+  p = fmaf(p, r, 0.6932609677314758f);
+  p = fmaf(p, r, 0.9999281167984009f);
+  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {

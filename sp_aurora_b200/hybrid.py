@@ -139,9 +139,7 @@ class LongContextAttention(torch.nn.Module):
                  attn_type: Union[str, AttnType] = AttnType.FA, use_pack_qkv: bool = False,
                  use_sync: bool = False):
         super().__init__()
-        if isinstance(attn_type, str):
-            attn_type = AttnType(attn_type)
-        self.attn_type = attn_type
+        self.attn_type = AttnType(attn_type)   # any reference or yunchang spelling; ignored
         ulysses_pg, ring_pg, u, r = _resolve_groups(ulysses_pg, ring_pg, sp_ulysses_degree,
                                                     sp_ring_degree)
         self.sp_ulysses_degree, self.sp_ring_degree = u, r
@@ -194,6 +192,7 @@ class LongContextAttentionQKVPacked(torch.nn.Module):
                  ulysses_pg=None, ring_pg=None, attn_type: Union[str, AttnType] = AttnType.FA,
                  use_sync: bool = False):
         super().__init__()
+        self.attn_type = AttnType(attn_type)   # any reference or yunchang spelling; ignored
         ulysses_pg, ring_pg, u, r = _resolve_groups(ulysses_pg, ring_pg, sp_ulysses_degree,
                                                     sp_ring_degree)
         self.ulysses_pg, self.ring_pg = (ulysses_pg if u > 1 else None), ring_pg

@@ -104,6 +104,12 @@ def check_qkv(q, k, v):
     return B, Sq, k.shape[1], Hq, Hkv, D
 
 
+def _check_rowstat(name: str, t: torch.Tensor, B: int, Hq: int, Sq: int):
+    """lse / delta: fp32 [B,Hq,Sq] with contiguous rows (batch and head strides are free)."""
+    if t.dtype != torch.float32 or tuple(t.shape) != (B, Hq, Sq) or (Sq > 1 and t.stride(2) != 1):
+        raise ValueError(f"{name} must be fp32 [B,Hq,Sq] with contiguous rows")
+
+
 def _fill_qkv(a, q, k, v):
     a.q, a.q_sb, a.q_ss, a.q_sh = q.data_ptr(), q.stride(0), q.stride(1), q.stride(2)
     a.k, a.k_sb, a.k_ss, a.k_sh = k.data_ptr(), k.stride(0), k.stride(1), k.stride(2)
@@ -113,8 +119,8 @@ def _fill_qkv(a, q, k, v):
 def attn_fwd_step(q, k, v, softmax_scale: float, causal: bool, lse: torch.Tensor,
                   out: Optional[torch.Tensor] = None, out_acc: Optional[torch.Tensor] = None,
                   merge_prev: bool = False, causal_off: int = 0) -> None:
-    """One spa_attn_fwd call. `lse` fp32 [B,Hq,Sq] is written (and read when
-    merge_prev); `out` (q.dtype, strided) and/or `out_acc` (fp32 contiguous)
+    """One spa_attn_fwd call. `lse` fp32 [B,Hq,Sq] (rows contiguous) is written (and
+    read when merge_prev); `out` (q.dtype, strided) and/or `out_acc` (fp32 contiguous)
     receive the (merged) rows."""
     B, Sq, Sk, Hq, Hkv, D = check_qkv(q, k, v)
     a = FwdArgs()
@@ -127,9 +133,8 @@ def attn_fwd_step(q, k, v, softmax_scale: float, causal: bool, lse: torch.Tensor
                 tuple(out_acc.shape) != (B, Sq, Hq, D):
             raise ValueError("out_acc must be contiguous fp32 [B,Sq,Hq,D]")
         a.out_acc = out_acc.data_ptr()
-    if lse.dtype != torch.float32 or not lse.is_contiguous() or tuple(lse.shape) != (B, Hq, Sq):
-        raise ValueError("lse must be contiguous fp32 [B,Hq,Sq]")
-    a.lse = lse.data_ptr()
+    _check_rowstat("lse", lse, B, Hq, Sq)
+    a.lse, a.lse_sb, a.lse_sh = lse.data_ptr(), lse.stride(0), lse.stride(1)
     a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.D = B, Sq, Sk, Hq, Hkv, D
     a.dtype = _lib.DTYPE_CODE[q.dtype]
     a.causal, a.causal_off, a.merge_prev = int(bool(causal)), int(causal_off), int(bool(merge_prev))
@@ -168,36 +173,63 @@ def bwd_delta(out: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
 
 
 def attn_bwd_step(q, k, v, dout, lse, delta, softmax_scale: float, causal: bool,
-                  dq_acc: torch.Tensor, dk: torch.Tensor, dv: torch.Tensor,
-                  dkv_accumulate: bool = False, causal_off: int = 0) -> None:
-    """One spa_attn_bwd call. dq_acc fp32 [B,Sq,Hq,D] is accumulated into;
-    dk/dv [B,Sk,Hkv,D] contiguous (fp32 or q.dtype) are overwritten or added to."""
+                  dq_acc: Optional[torch.Tensor], dk: Optional[torch.Tensor],
+                  dv: Optional[torch.Tensor], dkv_accumulate: bool = False, causal_off: int = 0,
+                  dq: Optional[torch.Tensor] = None, dq_overwrite: bool = False,
+                  deterministic: bool = False, passes: int = _lib.SPA_BWD_BOTH) -> None:
+    """One spa_attn_bwd call (see include/spa.h). The block's dQ plus the running sum in
+    dq_acc (fp32 [B,Sq,Hq,D] contiguous; ignored on input when dq_overwrite) is written to
+    dq (q.dtype, strided) and / or back to dq_acc. dk/dv [B,Sk,Hkv,D] are fp32 contiguous
+    or q.dtype (strided), overwritten or added to. `passes` runs only the dQ kernel or only
+    the dK/dV kernel of the pair."""
     B, Sq, Sk, Hq, Hkv, D = check_qkv(q, k, v)
     _check_tensor("dout", dout, q.dtype, q.device)
     a = BwdArgs()
     _fill_qkv(a, q, k, v)
     a.dout, a.do_sb, a.do_ss, a.do_sh = dout.data_ptr(), dout.stride(0), dout.stride(1), dout.stride(2)
-    for name, t in (("lse", lse), ("delta", delta)):
-        if t.dtype != torch.float32 or not t.is_contiguous() or tuple(t.shape) != (B, Hq, Sq):
-            raise ValueError(f"{name} must be contiguous fp32 [B,Hq,Sq]")
-    if dq_acc.dtype != torch.float32 or not dq_acc.is_contiguous() or \
-            tuple(dq_acc.shape) != (B, Sq, Hq, D):
-        raise ValueError("dq_acc must be contiguous fp32 [B,Sq,Hq,D]")
-    for name, t in (("dk", dk), ("dv", dv)):
-        if not t.is_contiguous() or tuple(t.shape) != (B, Sk, Hkv, D):
-            raise ValueError(f"{name} must be contiguous [B,Sk,Hkv,D]")
-        if t.dtype not in (torch.float32, q.dtype) or t.dtype != dk.dtype:
-            raise ValueError("dk/dv must both be fp32 or both q.dtype")
-    a.lse, a.delta, a.dq_acc = lse.data_ptr(), delta.data_ptr(), dq_acc.data_ptr()
-    a.dk, a.dv = dk.data_ptr(), dv.data_ptr()
-    a.dkv_fp32 = int(dk.dtype == torch.float32)
-    a.dkv_accumulate = int(bool(dkv_accumulate))
+    _check_rowstat("lse", lse, B, Hq, Sq)
+    _check_rowstat("delta", delta, B, Hq, Sq)
+    if lse.stride()[:2] != delta.stride()[:2]:
+        raise ValueError("lse and delta must share their batch and head strides")
+    a.lse, a.delta, a.lse_sb, a.lse_sh = lse.data_ptr(), delta.data_ptr(), lse.stride(0), lse.stride(1)
+    if passes != _lib.SPA_BWD_DKV_ONLY:
+        if dq_acc is not None:
+            if dq_acc.dtype != torch.float32 or not dq_acc.is_contiguous() or \
+                    tuple(dq_acc.shape) != (B, Sq, Hq, D):
+                raise ValueError("dq_acc must be contiguous fp32 [B,Sq,Hq,D]")
+            a.dq_acc = dq_acc.data_ptr()
+        if dq is not None:
+            _check_tensor("dq", dq, q.dtype, q.device)
+            if tuple(dq.shape) != (B, Sq, Hq, D):
+                raise ValueError("dq must be [B,Sq,Hq,D]")
+            a.dq, a.dq_sb, a.dq_ss, a.dq_sh = dq.data_ptr(), dq.stride(0), dq.stride(1), dq.stride(2)
+        if dq is None and dq_acc is None:
+            raise ValueError("one of dq / dq_acc is required")
+        if dq_acc is None and not dq_overwrite:
+            raise ValueError("accumulating dq needs dq_acc")
+        a.dq_overwrite = int(bool(dq_overwrite))
+    if passes != _lib.SPA_BWD_DQ_ONLY:
+        for name, t in (("dk", dk), ("dv", dv)):
+            if t is None or tuple(t.shape) != (B, Sk, Hkv, D) or t.stride(-1) != 1:
+                raise ValueError(f"{name} must be [B,Sk,Hkv,D] with a contiguous last dimension")
+            if t.dtype not in (torch.float32, q.dtype) or t.dtype != dk.dtype or t.stride() != dk.stride():
+                raise ValueError("dk/dv must both be fp32 or both q.dtype, with equal strides")
+        fp32_grads = dk.dtype == torch.float32 and q.dtype != torch.float32
+        if fp32_grads and not dk.is_contiguous():
+            raise ValueError("fp32 dk/dv of a 16-bit problem must be contiguous")
+        a.dk, a.dv = dk.data_ptr(), dv.data_ptr()
+        a.dkv_sb, a.dkv_ss, a.dkv_sh = dk.stride(0), dk.stride(1), dk.stride(2)
+        a.dkv_fp32 = int(fp32_grads)   # fp32 problems: fp32 is the element type
+        a.dkv_accumulate = int(bool(dkv_accumulate))
+    a.deterministic = int(bool(deterministic))
+    a.passes = int(passes)
     a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.D = B, Sq, Sk, Hq, Hkv, D
     a.dtype = _lib.DTYPE_CODE[q.dtype]
     a.causal, a.causal_off = int(bool(causal)), int(causal_off)
     a.scale = float(softmax_scale)
     a.stream = stream_ptr(q.device)
-    with _Timed("bwd", q.device, 2.5 * attn_flops(B, Sq, Sk, Hq, D, causal, causal_off)):
+    share = {_lib.SPA_BWD_BOTH: 2.5, _lib.SPA_BWD_DQ_ONLY: 1.0, _lib.SPA_BWD_DKV_ONLY: 1.5}[a.passes]
+    with _Timed("bwd", q.device, share * attn_flops(B, Sq, Sk, Hq, D, causal, causal_off)):
         check(lib.spa_attn_bwd(C.byref(a)), "spa_attn_bwd")
 
 
@@ -217,19 +249,49 @@ def cast_from_f32(src: torch.Tensor, dtype: torch.dtype, alpha: float = 1.0,
 
 
 def flash_attn_backward(dout, q, k, v, out, lse, softmax_scale: Optional[float] = None,
-                        causal: bool = False):
-    """Local attention backward: returns (dq, dk, dv) in q.dtype.
+                        causal: bool = False, dq: Optional[torch.Tensor] = None,
+                        dk: Optional[torch.Tensor] = None, dv: Optional[torch.Tensor] = None,
+                        deterministic: bool = False):
+    """Local attention backward: returns (dq, dk, dv) in q.dtype, written into the given
+    tensors when provided (any strides with a contiguous last dimension).
     Counterpart of sp_aurora/intel_flash_attn.py:129 intel_flash_attn_backward."""
     B, Sq, Sk, Hq, Hkv, D = check_qkv(q, k, v)
     if softmax_scale is None:
         softmax_scale = D ** -0.5
     delta = bwd_delta(out, dout)
-    dq_acc = torch.zeros((B, Sq, Hq, D), dtype=torch.float32, device=q.device)
-    dk = torch.empty((B, Sk, Hkv, D), dtype=q.dtype, device=q.device)
-    dv = torch.empty_like(dk)
-    attn_bwd_step(q, k, v, dout, lse, delta, softmax_scale, causal, dq_acc, dk, dv)
-    dq = dq_acc if q.dtype == torch.float32 else cast_from_f32(dq_acc, q.dtype)
+    if dq is None:
+        dq = torch.empty((B, Sq, Hq, D), dtype=q.dtype, device=q.device)
+    if dk is None:
+        dk = torch.empty((B, Sk, Hkv, D), dtype=q.dtype, device=q.device)
+    if dv is None:
+        dv = torch.empty((B, Sk, Hkv, D), dtype=q.dtype, device=q.device)
+    # each dq row, dk row and dv row has one owning CTA: no accumulator, nothing to zero
+    attn_bwd_step(q, k, v, dout, lse, delta, softmax_scale, causal, None, dk, dv,
+                  dq=dq, dq_overwrite=True, deterministic=deterministic)
     return dq, dk, dv
+
+
+class LocalFlashAttnFunc(torch.autograd.Function):
+    """Differentiable single-device attention on [B, S, H, D] tensors; returns (out, lse).
+    What sp_aurora/ulysses/attn_layer.py:34 select_flash_attn_impl hands to its callers."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, softmax_scale, causal):
+        if softmax_scale is None:
+            softmax_scale = q.shape[-1] ** -0.5
+        out, lse = flash_attn_forward(q, k, v, softmax_scale, causal)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.softmax_scale, ctx.causal = softmax_scale, causal
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, _dlse):
+        q, k, v, out, lse = ctx.saved_tensors
+        if dout.stride(-1) != 1:
+            dout = dout.contiguous()
+        dq, dk, dv = flash_attn_backward(dout, q, k, v, out, lse, ctx.softmax_scale, ctx.causal)
+        return dq, dk, dv, None, None
 
 
 def update_out_and_lse(out: Optional[torch.Tensor], lse: Optional[torch.Tensor],

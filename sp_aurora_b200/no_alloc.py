@@ -2,14 +2,14 @@
 
 `flash_attn_backward_noalloc` wraps the C entry point spa_attn_bwd_noalloc: the
 caller hands in every tensor, outputs included, and the library keeps its
-scratch (the fp32 dq accumulator and the delta row sums) in a fixed 64 MiB
-array that is part of the library image on each GPU. It exists for code that
-runs where all GPU memory is already spoken for (a pool that owns the device, a
-fixed-budget service) or that may not enter the CUDA allocator. Limits: the
-problem must satisfy B*Sq*Hq*(D+1)*4 bytes <= scratch_bytes(); calls share the
-one array, so two calls must not overlap on the same GPU; the first call on a
-device performs a one-time address lookup and should happen before any stream
-capture. It has no counterpart in the reference.
+scratch (the delta row sums, rowsum(dO * O)) in a fixed 16 MiB array that is
+part of the library image on each GPU. It exists for code that runs where all
+GPU memory is already spoken for (a pool that owns the device, a fixed-budget
+service) or that may not enter the CUDA allocator. Limits: the problem must
+satisfy B*Sq*Hq*4 bytes <= scratch_bytes(); calls share the one array, so two
+calls must not overlap on the same GPU; the first call on a device performs a
+one-time address lookup and should happen before any stream capture. It has no
+counterpart in the reference.
 """
 from __future__ import annotations
 

@@ -25,7 +25,7 @@ import torch.distributed as dist
 
 import os
 
-from . import local_attn, zigzag
+from . import _lib, local_attn, zigzag
 from .local_attn import check_unsupported_kwargs
 
 __all__ = [
@@ -157,61 +157,67 @@ def ring_flash_attn_backward(process_group, dout, q, k, v, out, softmax_lse, sof
                              causal: bool = True,
                              bwd_step: Callable = local_attn.attn_bwd_step,
                              delta_fn: Callable = local_attn.bwd_delta,
-                             cast_fn: Callable = local_attn.cast_from_f32):
+                             cast_fn: Callable = local_attn.cast_from_f32,
+                             deterministic: bool = False):
     """W-step backward ring. Returns (dq, dk, dv) in q.dtype.
     Counterpart of sp_aurora/intel_ring_flash_attn.py:153; algorithm of
-    sp_aurora/ring_flash_attn.py:70-154 (global out/lse, dK|dV ring of W hops)."""
+    sp_aurora/ring_flash_attn.py:70-154 (global out/lse, dK|dV ring of W hops).
+
+    Each step runs the dQ pass first and the dK/dV pass second: the travelling dK|dV
+    partial of the current block is still in flight during the dQ pass, and the dK/dV
+    pass then adds straight into the received buffer (no separate fold), which is sent on."""
     kv_comm = RingComm(process_group)
     d_kv_comm = RingComm(process_group)
     W, r = kv_comm.world_size, kv_comm.rank
     B, S, Hq, D = q.shape
     Hkv = k.shape[2]
     delta = delta_fn(out, dout)
-    dq_acc = torch.zeros((B, S, Hq, D), dtype=torch.float32, device=q.device)
+    dq = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device)
 
     if W == 1:
         dk = torch.empty((B, S, Hkv, D), dtype=q.dtype, device=q.device)
         dv = torch.empty_like(dk)
-        bwd_step(q, k, v, dout, softmax_lse, delta, softmax_scale, causal, dq_acc, dk, dv)
-        dq = dq_acc if q.dtype == torch.float32 else cast_fn(dq_acc, q.dtype)
+        bwd_step(q, k, v, dout, softmax_lse, delta, softmax_scale, causal, None, dk, dv,
+                 dq=dq, dq_overwrite=True, deterministic=deterministic)
         return dq, dk, dv
 
+    DQ, DKV = _lib.SPA_BWD_DQ_ONLY, _lib.SPA_BWD_DKV_ONLY
+    dq_acc = torch.empty((B, S, Hq, D), dtype=torch.float32, device=q.device)
+    last_step = r if causal else W - 1
     cur, axis = _pack_kv(k, v)
     kv_bufs = [torch.empty_like(cur), torch.empty_like(cur)]
-    # fp32 travelling partials, K|V gradients as one message [2,B,S,Hkv,D]. Each step's
-    # kernel writes into `local`; the partial that arrived with this K|V block is folded
-    # in after the kernel, so its transfer overlaps the kernel instead of preceding it.
-    local = torch.empty((2, B, S, Hkv, D), dtype=torch.float32, device=q.device)
-    dkv_bufs = [torch.empty_like(local) for _ in range(2)]
-    next_dkv = None
+    # fp32 travelling partials, K|V gradients as one message [2,B,S,Hkv,D]
+    dkv_bufs = [torch.empty((2, B, S, Hkv, D), dtype=torch.float32, device=q.device)
+                for _ in range(2)]
     for step in range(W):
         nxt = None
         if step + 1 != W:
             nxt = kv_comm.send_recv(cur, kv_bufs[step % 2])
             kv_comm.commit()
         computed = step <= r or not causal
+        kc, vc = (k, v) if step == 0 else _split_kv(cur, axis)
         if computed:
-            kc, vc = (k, v) if step == 0 else _split_kv(cur, axis)
-            tgt = dkv_bufs[0] if step == 0 else local     # step 0 starts the travelling sum
             bwd_step(q, kc, vc, dout, softmax_lse, delta, softmax_scale, causal and step == 0,
-                     dq_acc, tgt[0], tgt[1], dkv_accumulate=False)
-        if step == 0:
-            send = dkv_bufs[0]
-        else:
-            d_kv_comm.wait()
-            send = next_dkv
-            if computed:
-                send.add_(local)
+                     dq_acc if last_step > 0 else None, None, None,
+                     dq=dq if step == last_step else None, dq_overwrite=step == 0,
+                     deterministic=deterministic, passes=DQ)
+        tgt = dkv_bufs[step % 2]
+        if step > 0:
+            d_kv_comm.wait()           # the partial that travels with this block has arrived in tgt
+        if computed:
+            bwd_step(q, kc, vc, dout, softmax_lse, delta, softmax_scale, causal and step == 0,
+                     None, tgt[0], tgt[1], dkv_accumulate=step > 0,
+                     deterministic=deterministic, passes=DKV)
         if nxt is not None:
             kv_comm.wait()
             cur = nxt
-        recv = dkv_bufs[1] if send is dkv_bufs[0] else dkv_bufs[0]
-        next_dkv = d_kv_comm.send_recv(send, recv)
+        d_kv_comm.send_recv(tgt, dkv_bufs[(step + 1) % 2])
         d_kv_comm.commit()
     d_kv_comm.wait()
+    home = dkv_bufs[W % 2]
     if q.dtype == torch.float32:
-        return dq_acc, next_dkv[0], next_dkv[1]
-    return cast_fn(dq_acc, q.dtype), cast_fn(next_dkv[0], q.dtype), cast_fn(next_dkv[1], q.dtype)
+        return dq, home[0], home[1]
+    return dq, cast_fn(home[0], q.dtype), cast_fn(home[1], q.dtype)
 
 
 def _use_zigzag(group, q, causal) -> bool:
@@ -245,6 +251,7 @@ class RingFlashAttnFunc(torch.autograd.Function):
         ctx.softmax_scale = softmax_scale
         ctx.causal = causal
         ctx.group = group
+        ctx.deterministic = bool(deterministic)
         return out if not return_softmax else (out, lse, None)
 
     @staticmethod
@@ -254,11 +261,13 @@ class RingFlashAttnFunc(torch.autograd.Function):
         if ctx.zigzag:
             q_z, kv_z, out_z, lse_z = ctx.saved_tensors
             dq, dk, dv = zigzag.zigzag_ring_backward(ctx.group, dout, q_z, kv_z, out_z, lse_z,
-                                                     ctx.softmax_scale)
+                                                     ctx.softmax_scale,
+                                                     deterministic=ctx.deterministic)
             return dq, dk, dv, None, None, None, None, None, None, None, None
         q, k, v, out, lse = ctx.saved_tensors
         dq, dk, dv = ring_flash_attn_backward(ctx.group, dout, q, k, v, out, lse,
-                                              ctx.softmax_scale, ctx.causal)
+                                              ctx.softmax_scale, ctx.causal,
+                                              deterministic=ctx.deterministic)
         return dq, dk, dv, None, None, None, None, None, None, None, None
 
 

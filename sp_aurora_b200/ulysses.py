@@ -18,13 +18,15 @@ import torch
 import torch.distributed as dist
 
 from . import local_attn
-from .all_to_all import SeqAllToAll4D, all_to_all_4D, reshard_lse
+from .all_to_all import (SeqAllToAll4D, all_to_all_4D, heads_all_to_all_packed, reshard_lse,
+                         seq_all_to_all_packed)
 from .local_attn import check_unsupported_kwargs
 
 __all__ = [
     "ulysses_flash_attn_forward", "ulysses_flash_attn_backward", "UlyssesFlashAttnFunc",
     "ulysses_flash_attn_func", "ulysses_flash_attn_kvpacked_func",
-    "ulysses_flash_attn_qkvpacked_func", "UlyssesAttention", "AttnType",
+    "ulysses_flash_attn_qkvpacked_func", "UlyssesAttention", "AttnType", "UlyssesComm",
+    "select_flash_attn_impl",
 ]
 
 
@@ -36,15 +38,15 @@ def _group_size(group) -> int:
 
 def ulysses_flash_attn_forward(process_group, q, k, v, softmax_scale: float, causal: bool = False):
     """Returns (out [B,S_loc,Hq,D], lse [B,Hq,S_loc], saved) where `saved` holds
-    the head-sharded q, k, v, out, lse for backward."""
+    the head-sharded q, k, v, out, lse for backward. q, k and v travel as one
+    all-to-all message (the reference sends three, sp_aurora/intel_ulysses_attn.py:156-170)
+    and are read by the attention kernel where they land."""
     P = _group_size(process_group)
     if P > 1 and (q.shape[2] % P or k.shape[2] % P):
         raise ValueError(
             f"q heads ({q.shape[2]}) and kv heads ({k.shape[2]}) must be divisible by the "
             f"Ulysses group size ({P})")
-    q_r = all_to_all_4D(q, 2, 1, group=process_group)
-    k_r = all_to_all_4D(k, 2, 1, group=process_group)
-    v_r = all_to_all_4D(v, 2, 1, group=process_group)
+    q_r, k_r, v_r = heads_all_to_all_packed((q, k, v), group=process_group)
     out_r, lse_r = local_attn.flash_attn_forward(q_r, k_r, v_r, softmax_scale, causal)
     out = all_to_all_4D(out_r, 1, 2, group=process_group)
     lse = reshard_lse(lse_r, process_group)
@@ -53,13 +55,17 @@ def ulysses_flash_attn_forward(process_group, q, k, v, softmax_scale: float, cau
 
 def ulysses_flash_attn_backward(process_group, dout, q_r, k_r, v_r, out_r, lse_r,
                                 softmax_scale: float, causal: bool = False):
-    """Returns (dq, dk, dv) sharded on sequence like the inputs of forward."""
+    """Returns (dq, dk, dv) sharded on sequence like the inputs of forward. The three
+    gradients are written by the kernels into one [B, S, hq+2*hkv, D] buffer and go back
+    as one all-to-all message."""
     dout_r = all_to_all_4D(dout, 2, 1, group=process_group)
-    dq_r, dk_r, dv_r = local_attn.flash_attn_backward(dout_r, q_r, k_r, v_r, out_r, lse_r,
-                                                      softmax_scale, causal)
-    dq = all_to_all_4D(dq_r, 1, 2, group=process_group)
-    dk = all_to_all_4D(dk_r, 1, 2, group=process_group)
-    dv = all_to_all_4D(dv_r, 1, 2, group=process_group)
+    B, S, hq, D = q_r.shape
+    hkv = k_r.shape[2]
+    grads = torch.empty((B, S, hq + 2 * hkv, D), dtype=q_r.dtype, device=q_r.device)
+    dq_r, dk_r, dv_r = grads[:, :, :hq], grads[:, :, hq:hq + hkv], grads[:, :, hq + hkv:]
+    local_attn.flash_attn_backward(dout_r, q_r, k_r, v_r, out_r, lse_r, softmax_scale, causal,
+                                   dq=dq_r, dk=dk_r, dv=dv_r)
+    dq, dk, dv = seq_all_to_all_packed((dq_r, dk_r, dv_r), group=process_group)
     return dq, dk, dv
 
 
@@ -118,23 +124,64 @@ def ulysses_flash_attn_qkvpacked_func(qkv, dropout_p=0.0, softmax_scale=None, ca
                                       deterministic, return_attn_probs, group)
 
 
-class AttnType(Enum):
-    """Accepted for signature compatibility with sp_aurora/ulysses/attn_layer.py:20;
-    every value runs the same sm_100a kernels (there is no backend selection)."""
-    FA = "fa"
-    FA3 = "fa3"
+class AttnType(str, Enum):
+    """Attention backend names of sp_aurora/ulysses/attn_layer.py:20-31 (a str enum with
+    the same members and values). Every value runs the same sm_100a kernels: there is no
+    backend selection here, the argument is accepted and ignored. The yunchang spellings
+    ("fa", "fa3", "sage_*", "sparse_sage") are accepted as aliases of FA."""
     TORCH = "torch"
-    SAGE_AUTO = "sage_auto"
-    SAGE_FP16 = "sage_fp16"
-    SAGE_FP8 = "sage_fp8"
-    SPARSE_SAGE = "sparse_sage"
+    INTEL_SYCL = "intel_sycl"
+    INTEL_ONEDNN = "intel_onednn"
+    FA = "flash_attn"
+    FA3 = "flash_attn_3"
+
+    @classmethod
+    def _missing_(cls, value):
+        aliases = {"fa": cls.FA, "fa3": cls.FA3, "sage_auto": cls.FA, "sage_fp16": cls.FA,
+                   "sage_fp8": cls.FA, "sparse_sage": cls.FA}
+        if isinstance(value, str) and value.lower() in aliases:
+            return aliases[value.lower()]
+        return None
 
     @classmethod
     def from_string(cls, s: str):
-        for member in cls:
-            if member.value == s:
-                return member
-        raise ValueError(f"'{s}' is not a valid {cls.__name__}")
+        return cls(s)
+
+
+def select_flash_attn_impl(attn_type: "AttnType" = AttnType.FA):
+    """Counterpart of sp_aurora/ulysses/attn_layer.py:34 select_flash_attn_impl: returns
+    the local attention function `fn(q, k, v, dropout_p=0.0, softmax_scale=None,
+    causal=False, window_size=(-1, -1), softcap=0.0, alibi_slopes=None,
+    deterministic=False, return_attn_probs=False)` on [B, S, H, D] tensors. Every
+    `attn_type` selects the same sm_100a kernels; with return_attn_probs the second
+    result is lse [B, H, S] fp32."""
+    AttnType(attn_type)   # raises ValueError on an unknown name, like the enum lookup would
+
+    def attn_fn(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
+                softcap=0.0, alibi_slopes=None, deterministic=False, return_attn_probs=False):
+        check_unsupported_kwargs(dropout_p, window_size, alibi_slopes, softcap)
+        out, lse = local_attn.LocalFlashAttnFunc.apply(q, k, v, softmax_scale, causal)
+        return (out, lse) if return_attn_probs else out
+
+    return attn_fn
+
+
+class UlyssesComm:
+    """Counterpart of sp_aurora/intel_ulysses_attn.py:146 IntelUlyssesComm: the two
+    reshards of Ulysses attention as methods (autograd-aware)."""
+
+    def __init__(self, process_group: Optional[dist.ProcessGroup] = None):
+        self.process_group = process_group
+        live = dist.is_available() and dist.is_initialized()
+        self.world_size = dist.get_world_size(process_group) if live else 1
+        self.rank = dist.get_rank(process_group) if live else 0
+
+    def all_to_all_qkv(self, q, k, v, scatter_idx: int = 2, gather_idx: int = 1):
+        return tuple(SeqAllToAll4D.apply(self.process_group, t, scatter_idx, gather_idx)
+                     for t in (q, k, v))
+
+    def all_to_all_output(self, output, scatter_idx: int = 1, gather_idx: int = 2):
+        return SeqAllToAll4D.apply(self.process_group, output, scatter_idx, gather_idx)
 
 
 class UlyssesAttention(torch.nn.Module):
@@ -151,7 +198,7 @@ class UlyssesAttention(torch.nn.Module):
         self.scatter_idx = scatter_idx
         self.gather_idx = gather_idx
         self.use_sync = use_sync
-        self.attn_type = attn_type
+        self.attn_type = AttnType(attn_type)   # any reference or yunchang spelling; ignored
 
     def forward(self, query, key, value, dropout_p=0.0, softmax_scale=None, causal=False,
                 window_size=(-1, -1), softcap=0.0, alibi_slopes=None, deterministic=False,

@@ -13,9 +13,13 @@ Per step, with the K|V pair that started on rank src = (r - step) mod W
   step 0  : (q0,k0) causal, (q1,k0) full, (q1,k1) causal
   src < r : (q0,k0) full,   (q1,k0) full          (k1 is later than both)
   src > r : (q1,k0) full,   (q1,k1) full          (q0 is earlier than both)
-Internal layouts keep the half index outermost so every call sees contiguous
-[B, S/2, H, D] operands: q_z [2,B,h,Hq,D]; K|V message [2(half),2(k|v),B,h,Hkv,D];
-lse_z [2,B,Hq,h]; accumulators alike.
+For batch size 1 the two halves of a tensor are adjacent rows of one [1, 2h, H, D]
+tensor, and calls that share a query or key operand are merged into one launch:
+  step 0  : (q1,[k0;k1]) causal with offset h,  (q0,k0) causal
+  src < r : ([q0;q1],k0) full
+  src > r : (q1,[k0;k1]) full
+Internal layouts: q_z, out_z, accumulators [2(half),B,h,Hq,D]; K|V message
+[2(k|v),2(half),B,h,Hkv,D]; lse_z, delta_z [B,Hq,2(half),h].
 """
 from __future__ import annotations
 
@@ -24,7 +28,7 @@ from typing import Callable, List, Sequence, Tuple
 import torch
 import torch.distributed as dist
 
-from . import local_attn
+from . import _lib, local_attn
 
 
 def _group_info(group):
@@ -45,7 +49,8 @@ def exchange_halves(pairs: Sequence[Tuple[List[torch.Tensor], List[torch.Tensor]
     """Move half-chunks between the contiguous layout (rank r holds half-chunks
     2r, 2r+1) and the zigzag layout (rank r holds r, 2W-1-r).
 
-    `pairs` is a list of (src_halves, dst_halves): two contiguous tensors each.
+    `pairs` is a list of (src_halves, dst_halves): two tensors each; sources must be
+    contiguous, destinations may be strided views (received through a staging tensor).
     to_zigzag=True : src_halves[i] is half-chunk 2r+i, dst_halves[j] receives slot j.
     to_zigzag=False: src_halves[j] is slot j, dst_halves[i] receives half-chunk 2r+i.
     All transfers of all pairs go out as one batched group (ordered per peer)."""
@@ -57,7 +62,16 @@ def exchange_halves(pairs: Sequence[Tuple[List[torch.Tensor], List[torch.Tensor]
         return
     r, W = _group_info(group)
     ops = []
-    local = []
+    local = []       # (dst, src) copies that can run at once
+    after = []       # (dst, staging) copies that wait for their receive
+
+    def recv_into(view, peer):
+        tgt = view
+        if not view.is_contiguous():
+            tgt = torch.empty(view.shape, dtype=view.dtype, device=view.device)
+            after.append((view, tgt))
+        ops.append(dist.P2POp(dist.irecv, tgt, _global(group, peer), group=group))
+
     for src, dst in pairs:
         for i in range(2):
             c = 2 * r + i                      # half-chunk living here in contiguous layout
@@ -71,14 +85,14 @@ def exchange_halves(pairs: Sequence[Tuple[List[torch.Tensor], List[torch.Tensor]
                 if zr == r:
                     local.append((dst[i], src[zs]))
                 else:
-                    ops.append(dist.P2POp(dist.irecv, dst[i], _global(group, zr), group=group))
+                    recv_into(dst[i], zr)
         for j in range(2):
             c = r if j == 0 else 2 * W - 1 - r  # half-chunk living here in zigzag layout
             cr = c // 2                         # its rank in contiguous layout
             if cr == r:
                 continue                        # handled as a local copy above
             if to_zigzag:
-                ops.append(dist.P2POp(dist.irecv, dst[j], _global(group, cr), group=group))
+                recv_into(dst[j], cr)
             else:
                 ops.append(dist.P2POp(dist.isend, src[j], _global(group, cr), group=group))
     reqs = dist.batch_isend_irecv(ops) if ops else []
@@ -86,22 +100,61 @@ def exchange_halves(pairs: Sequence[Tuple[List[torch.Tensor], List[torch.Tensor]
         d.copy_(s)
     for req in reqs:
         req.wait()
+    for d, s in after:
+        d.copy_(s)
 
 
 def _halves(x: torch.Tensor) -> List[torch.Tensor]:
-    """Two contiguous [B, S/2, ...] halves of a [B, S, ...] tensor."""
+    """The two [B, S/2, ...] halves of a [B, S, ...] tensor, contiguous (views when the
+    batch size is 1, copies otherwise)."""
     h = x.shape[1] // 2
     return [x[:, :h].contiguous(), x[:, h:].contiguous()]
 
 
 def _step_calls(step: int, r: int, W: int):
-    """(q_half, k_half, causal) calls of one ring step (see module docstring)."""
+    """(q_half, k_half, causal) blocks of one ring step (see module docstring)."""
     src = (r - step) % W
     if step == 0:
         return [(0, 0, True), (1, 0, False), (1, 1, True)]
     if src < r:
         return [(0, 0, False), (1, 0, False)]
     return [(1, 0, False), (1, 1, False)]
+
+
+def _plan(step: int, r: int, W: int, merged: bool):
+    """Kernel calls of one ring step as (q_lo, q_n, k_lo, k_n, causal, offset_halves):
+    query halves [q_lo, q_lo+q_n) against key halves [k_lo, k_lo+k_n); a causal call
+    lets query i see key j <= i + offset_halves*h. Within a step, a call that overwrites
+    the dK/dV of a key half precedes the calls that add to it."""
+    src = (r - step) % W
+    if merged:
+        if step == 0:
+            return [(1, 1, 0, 2, True, 1), (0, 1, 0, 1, True, 0)]
+        if src < r:
+            return [(0, 2, 0, 1, False, 0)]
+        return [(1, 1, 0, 2, False, 0)]
+    if step == 0:
+        return [(1, 1, 0, 1, False, 0), (1, 1, 1, 1, True, 0), (0, 1, 0, 1, True, 0)]
+    if src < r:
+        return [(0, 1, 0, 1, False, 0), (1, 1, 0, 1, False, 0)]
+    return [(1, 1, 0, 1, False, 0), (1, 1, 1, 1, False, 0)]
+
+
+def _rows(x_z: torch.Tensor, lo: int, n: int) -> torch.Tensor:
+    """Halves [lo, lo+n) of a [2, B, h, H, D] tensor as one [B, n*h, H, D] tensor
+    (n == 2 only for batch size 1, where the halves are adjacent rows)."""
+    if n == 1:
+        return x_z[lo]
+    _, B, h, H, D = x_z.shape
+    return x_z.view(B, 2 * h, H, D)
+
+
+def _stat_rows(s_z: torch.Tensor, lo: int, n: int) -> torch.Tensor:
+    """Halves [lo, lo+n) of a [B, Hq, 2, h] row-statistics tensor as [B, Hq, n*h]."""
+    if n == 1:
+        return s_z[:, :, lo]
+    B, Hq, _, h = s_z.shape
+    return s_z.view(B, Hq, 2 * h)
 
 
 def zigzag_ring_forward(group, q, k, v, softmax_scale: float,
@@ -120,16 +173,17 @@ def zigzag_ring_forward(group, q, k, v, softmax_scale: float,
     h = S // 2
     dev, dt = q.device, q.dtype
     q_z = torch.empty((2, B, h, Hq, D), dtype=dt, device=dev)
-    kv_z = torch.empty((2, 2, B, h, Hkv, D), dtype=dt, device=dev)
+    kv_z = torch.empty((2, 2, B, h, Hkv, D), dtype=dt, device=dev)      # [k|v][half]
     exchange_halves([(_halves(q), [q_z[0], q_z[1]]),
-                     (_halves(k), [kv_z[0, 0], kv_z[1, 0]]),
-                     (_halves(v), [kv_z[0, 1], kv_z[1, 1]])], group, to_zigzag=True)
+                     (_halves(k), [kv_z[0, 0], kv_z[0, 1]]),
+                     (_halves(v), [kv_z[1, 0], kv_z[1, 1]])], group, to_zigzag=True)
 
     out_z = torch.empty((2, B, h, Hq, D), dtype=dt, device=dev)
     acc_z = torch.empty((2, B, h, Hq, D), dtype=torch.float32, device=dev)
-    lse_z = torch.empty((2, B, Hq, h), dtype=torch.float32, device=dev)
-    plan = [_step_calls(s, r, W) for s in range(W)]
-    n_calls = [sum(1 for st in plan for c in st if c[0] == qh) for qh in (0, 1)]
+    lse_z = torch.empty((B, Hq, 2, h), dtype=torch.float32, device=dev)
+    merged = B == 1
+    plan = [_plan(s, r, W, merged) for s in range(W)]
+    n_calls = [sum(1 for st in plan for c in st if c[0] <= qh < c[0] + c[1]) for qh in (0, 1)]
     done = [0, 0]
     bufs = [torch.empty_like(kv_z), torch.empty_like(kv_z)]
     cur = kv_z
@@ -138,39 +192,44 @@ def zigzag_ring_forward(group, q, k, v, softmax_scale: float,
         if step + 1 != W:
             nxt = comm.send_recv(cur, bufs[step % 2])
             comm.commit()
-        for qh, kh, causal in plan[step]:
-            first, last = done[qh] == 0, done[qh] + 1 == n_calls[qh]
-            fwd_step(q_z[qh], cur[kh, 0], cur[kh, 1], softmax_scale, causal, lse_z[qh],
-                     out=out_z[qh] if last else None,
-                     out_acc=None if (first and last) else acc_z[qh], merge_prev=not first)
-            done[qh] += 1
+        for q_lo, q_n, k_lo, k_n, causal, off in plan[step]:
+            halves = range(q_lo, q_lo + q_n)
+            first = done[q_lo] == 0                       # the same for every half of a call
+            last_any = any(done[i] + 1 == n_calls[i] for i in halves)
+            last_all = all(done[i] + 1 == n_calls[i] for i in halves)
+            fwd_step(_rows(q_z, q_lo, q_n), _rows(cur[0], k_lo, k_n), _rows(cur[1], k_lo, k_n),
+                     softmax_scale, causal, _stat_rows(lse_z, q_lo, q_n),
+                     out=_rows(out_z, q_lo, q_n) if last_any else None,
+                     out_acc=None if (first and last_all) else _rows(acc_z, q_lo, q_n),
+                     merge_prev=not first, causal_off=off * h)
+            for i in halves:
+                done[i] += 1
         if nxt is not None:
             comm.wait()
             cur = nxt
 
     out = torch.empty((B, S, Hq, D), dtype=dt, device=dev)
-    o_dst = [torch.empty((B, h, Hq, D), dtype=dt, device=dev) for _ in range(2)]
-    pairs = [([out_z[0], out_z[1]], o_dst)]
+    pairs = [([out_z[0], out_z[1]], [out[:, :h], out[:, h:]])]
     lse = None
     if need_lse:     # the backward uses lse_z; the contiguous lse is only for the caller
         lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
-        l_dst = [torch.empty((B, Hq, h), dtype=torch.float32, device=dev) for _ in range(2)]
-        pairs.append(([lse_z[0], lse_z[1]], l_dst))
+        pairs.append(([lse_z[:, :, 0].contiguous(), lse_z[:, :, 1].contiguous()],
+                      [lse[:, :, :h], lse[:, :, h:]]))
     exchange_halves(pairs, group, to_zigzag=False)
-    out[:, :h].copy_(o_dst[0])
-    out[:, h:].copy_(o_dst[1])
-    if need_lse:
-        lse[:, :, :h].copy_(l_dst[0])
-        lse[:, :, h:].copy_(l_dst[1])
     return out, lse, (q_z, kv_z, out_z, lse_z)
 
 
 def zigzag_ring_backward(group, dout, q_z, kv_z, out_z, lse_z, softmax_scale: float,
                          bwd_step: Callable = local_attn.attn_bwd_step,
                          delta_fn: Callable = local_attn.bwd_delta,
-                         cast_fn: Callable = local_attn.cast_from_f32):
+                         cast_fn: Callable = local_attn.cast_from_f32,
+                         deterministic: bool = False):
     """Backward of zigzag_ring_forward. `dout` is the contiguous shard; returns
-    (dq, dk, dv) as contiguous shards in q's dtype."""
+    (dq, dk, dv) as contiguous shards in q's dtype.
+
+    Each step runs its dQ passes first and its dK/dV passes second: the travelling dK|dV
+    partial of the current block is still in flight during the dQ passes, and the dK/dV
+    passes then add straight into the received buffer, which is sent on."""
     from .ring import RingComm
     kv_comm = RingComm(group)
     d_kv_comm = RingComm(group)
@@ -178,59 +237,74 @@ def zigzag_ring_backward(group, dout, q_z, kv_z, out_z, lse_z, softmax_scale: fl
     _, B, h, Hq, D = q_z.shape
     Hkv = kv_z.shape[4]
     dev, dt = q_z.device, q_z.dtype
+    DQ, DKV = _lib.SPA_BWD_DQ_ONLY, _lib.SPA_BWD_DKV_ONLY
     do_z = torch.empty((2, B, h, Hq, D), dtype=dt, device=dev)
     exchange_halves([(_halves(dout), [do_z[0], do_z[1]])], group, to_zigzag=True)
-    delta_z = [delta_fn(out_z[i], do_z[i]) for i in range(2)]
-    dq_acc = torch.zeros((2, B, h, Hq, D), dtype=torch.float32, device=dev)
-    # dK|dV: each step's kernels write into `local`; the partial that travelled here
-    # with the K|V block is folded in AFTER the kernels (so its transfer overlaps
-    # them) and the sum is sent on. Layout [2(half), 2(k|v), B, h, Hkv, D] fp32.
-    local = torch.empty((2, 2, B, h, Hkv, D), dtype=torch.float32, device=dev)
-    dkv_bufs = [torch.empty_like(local) for _ in range(3)]
+    merged = B == 1
+    if merged:
+        delta_z = delta_fn(_rows(out_z, 0, 2), _rows(do_z, 0, 2)).view(B, Hq, 2, h)
+    else:
+        delta_z = torch.empty((B, Hq, 2, h), dtype=torch.float32, device=dev)
+        for i in range(2):
+            delta_z[:, :, i].copy_(delta_fn(out_z[i], do_z[i]))
+    dq_acc = torch.empty((2, B, h, Hq, D), dtype=torch.float32, device=dev)
+    dq_z = torch.empty((2, B, h, Hq, D), dtype=dt, device=dev)
+    plan = [_plan(s, r, W, merged) for s in range(W)]
+    n_calls = [sum(1 for st in plan for c in st if c[0] <= qh < c[0] + c[1]) for qh in (0, 1)]
+    done = [0, 0]
+    # fp32 travelling partials [2(k|v), 2(half), B, h, Hkv, D], one message
+    dkv_bufs = [torch.empty((2, 2, B, h, Hkv, D), dtype=torch.float32, device=dev) for _ in range(2)]
     kv_bufs = [torch.empty_like(kv_z), torch.empty_like(kv_z)]
     cur = kv_z
-    next_dkv = None
     for step in range(W):
         nxt = None
         if step + 1 != W:
             nxt = kv_comm.send_recv(cur, kv_bufs[step % 2])
             kv_comm.commit()
-        written = [False, False]
-        tgt = dkv_bufs[0] if step == 0 else local   # step 0 (both key halves) starts the sum
-        for qh, kh, causal in _step_calls(step, r, W):
-            bwd_step(q_z[qh], cur[kh, 0], cur[kh, 1], do_z[qh], lse_z[qh], delta_z[qh],
-                     softmax_scale, causal, dq_acc[qh], tgt[kh, 0], tgt[kh, 1],
-                     dkv_accumulate=written[kh])
-            written[kh] = True
-        if step == 0:
-            send = dkv_bufs[0]
-        else:
-            d_kv_comm.wait()           # partial for this block, sent during the previous step
-            send = next_dkv
-            for kh in range(2):
-                if written[kh]:
-                    send[kh].add_(local[kh])
+        for q_lo, q_n, k_lo, k_n, causal, off in plan[step]:
+            halves = range(q_lo, q_lo + q_n)
+            first = done[q_lo] == 0
+            last_any = any(done[i] + 1 == n_calls[i] for i in halves)
+            bwd_step(_rows(q_z, q_lo, q_n), _rows(cur[0], k_lo, k_n), _rows(cur[1], k_lo, k_n),
+                     _rows(do_z, q_lo, q_n), _stat_rows(lse_z, q_lo, q_n),
+                     _stat_rows(delta_z, q_lo, q_n), softmax_scale, causal,
+                     _rows(dq_acc, q_lo, q_n), None, None, causal_off=off * h,
+                     dq=_rows(dq_z, q_lo, q_n) if last_any else None, dq_overwrite=first,
+                     deterministic=deterministic, passes=DQ)
+            for i in halves:
+                done[i] += 1
+        tgt = dkv_bufs[step % 2]
+        if step > 0:
+            d_kv_comm.wait()           # the partial that travels with this block has arrived in tgt
+        written = [step > 0, step > 0]
+        for q_lo, q_n, k_lo, k_n, causal, off in plan[step]:
+            khalves = range(k_lo, k_lo + k_n)
+            bwd_step(_rows(q_z, q_lo, q_n), _rows(cur[0], k_lo, k_n), _rows(cur[1], k_lo, k_n),
+                     _rows(do_z, q_lo, q_n), _stat_rows(lse_z, q_lo, q_n),
+                     _stat_rows(delta_z, q_lo, q_n), softmax_scale, causal,
+                     None, _rows(tgt[0], k_lo, k_n), _rows(tgt[1], k_lo, k_n),
+                     dkv_accumulate=written[k_lo], causal_off=off * h,
+                     deterministic=deterministic, passes=DKV)
+            for i in khalves:
+                written[i] = True
         if nxt is not None:
             kv_comm.wait()
             cur = nxt
-        recv = dkv_bufs[(step + 1) % 3]
-        next_dkv = d_kv_comm.send_recv(send, recv)
+        d_kv_comm.send_recv(tgt, dkv_bufs[(step + 1) % 2])
         d_kv_comm.commit()
     d_kv_comm.wait()
+    home = dkv_bufs[W % 2]
 
     def to_dt(x):  # fp32 [B,h,H,D] -> dt
         return x if dt == torch.float32 else cast_fn(x, dt)
 
-    dq_h = [to_dt(dq_acc[i]) for i in range(2)]
-    dk_h = [to_dt(next_dkv[i, 0]) for i in range(2)]
-    dv_h = [to_dt(next_dkv[i, 1]) for i in range(2)]
+    dk_h = [to_dt(home[0, i]) for i in range(2)]
+    dv_h = [to_dt(home[1, i]) for i in range(2)]
     S = 2 * h
     dq = torch.empty((B, S, Hq, D), dtype=dt, device=dev)
     dk = torch.empty((B, S, Hkv, D), dtype=dt, device=dev)
     dv = torch.empty((B, S, Hkv, D), dtype=dt, device=dev)
-    dst = [[torch.empty_like(t[0]), torch.empty_like(t[1])] for t in (dq_h, dk_h, dv_h)]
-    exchange_halves([(dq_h, dst[0]), (dk_h, dst[1]), (dv_h, dst[2])], group, to_zigzag=False)
-    for full, halves in ((dq, dst[0]), (dk, dst[1]), (dv, dst[2])):
-        full[:, :h].copy_(halves[0])
-        full[:, h:].copy_(halves[1])
+    exchange_halves([([dq_z[0], dq_z[1]], [dq[:, :h], dq[:, h:]]),
+                     (dk_h, [dk[:, :h], dk[:, h:]]),
+                     (dv_h, [dv[:, :h], dv[:, h:]])], group, to_zigzag=False)
     return dq, dk, dv

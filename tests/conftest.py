@@ -17,6 +17,16 @@ def golden_dir():
     return os.path.join(ROOT, "tests", "golden")
 
 
-def pytest_collection_modifyitems(config, items):
-    # GPU tests fail loudly (not skip) on a machine that selected them without a GPU.
-    pass
+@pytest.fixture(scope="session")
+def error_log():
+    """Measured max-abs errors of the GPU parity cases, written to
+    gpurun_out/parity_errors.json at the end of the session (and printed with -s)."""
+    import json
+    log = {}
+    yield log
+    if log:
+        out_dir = os.path.join(ROOT, "gpurun_out")
+        os.makedirs(out_dir, exist_ok=True)
+        with open(os.path.join(out_dir, "parity_errors.json"), "w") as f:
+            json.dump(log, f, indent=1, sort_keys=True)
+        print("\nparity errors:", json.dumps(log, sort_keys=True))

@@ -43,15 +43,23 @@ def _check_fwd(spa, B, Sq, Sk, Hq, Hkv, D, dtype, causal, seed=0):
     return q, k, v, out, lse, ref_out, ref_lse
 
 
-def _check_bwd(spa, q, k, v, out, lse, ref_out, ref_lse, dtype, causal, seed=0):
+def grad_tol(dtype, want):
+    """Gradient bound: the stated max-abs tolerance while |gradient| <= 4. A 16-bit output
+    of magnitude x carries a rounding error of up to x * 2^-9 on its own, which passes 2e-2
+    at x ~ 10, so beyond 4 the bound grows in proportion (2e-2 * max|ref| / 4)."""
+    return TOL[dtype] * max(1.0, want.abs().max().item() / 4)
+
+
+def _check_bwd(spa, q, k, v, out, lse, ref_out, ref_lse, dtype, causal, seed=0, record=None):
     dout = _rand(tuple(q.shape), dtype, seed + 3)
     dq, dk, dv = spa.flash_attn_backward(dout.cuda(), q.cuda(), k.cuda(), v.cuda(), out, lse, None, causal)
     spa.check_status()
     rdq, rdk, rdv = orc.attention_bwd_ref(dout, q, k, v, ref_out, ref_lse, None, causal)
     for name, got, want in (("dq", dq, rdq), ("dk", dk, rdk), ("dv", dv, rdv)):
         err = (got.cpu().double() - want).abs().max().item()
-        scale = max(1.0, want.abs().max().item() / 4)     # gradients of O(10) keep relative meaning
-        assert err <= TOL[dtype] * scale, f"{name} err {err} (max |ref| {want.abs().max().item()})"
+        if record is not None:
+            record[name] = (err, want.abs().max().item())
+        assert err <= grad_tol(dtype, want), f"{name} err {err} (max |ref| {want.abs().max().item()})"
 
 
 # fp32 runs on the CUDA-core kernel: reference-test shapes (D 32/64/128, ragged, GQA)
@@ -77,9 +85,68 @@ TC_CASES = [
 
 
 @pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D,causal", TC_CASES)
-def test_bf16_forward_backward(spa, B, Sq, Sk, Hq, Hkv, D, causal):
+def test_bf16_forward_backward(spa, B, Sq, Sk, Hq, Hkv, D, causal, error_log):
     r = _check_fwd(spa, B, Sq, Sk, Hq, Hkv, D, torch.bfloat16, causal)
-    _check_bwd(spa, *r, torch.bfloat16, causal)
+    rec = {}
+    _check_bwd(spa, *r, torch.bfloat16, causal, record=rec)
+    error_log[f"bf16 B{B} Sq{Sq} Sk{Sk} Hq{Hq} Hkv{Hkv} D{D} causal{int(causal)}"] = {
+        k: {"err": e, "max_ref": m, "strict_2e-2": e <= 2e-2} for k, (e, m) in rec.items()}
+
+
+def test_backward_is_bitwise_reproducible(spa):
+    """Every dq, dk and dv row has one owning CTA and a fixed summation order: two runs on
+    the same inputs give identical bits (also with deterministic=True, which only forbids
+    the split of a K/V tile's queries between CTAs in the fp32-gradient ring steps)."""
+    from sp_aurora_b200 import local_attn as la
+    B, S, Hq, Hkv, D = 1, 2048, 8, 2, 128
+    q, k, v, do = (_rand(sh, torch.bfloat16, s).cuda() for sh, s in (
+        ((B, S, Hq, D), 1), ((B, S, Hkv, D), 2), ((B, S, Hkv, D), 3), ((B, S, Hq, D), 4)))
+    out, lse = spa.flash_attn_forward(q, k, v, None, True)
+    out2, lse2 = spa.flash_attn_forward(q, k, v, None, True)
+    assert torch.equal(out, out2) and torch.equal(lse, lse2)
+    a = spa.flash_attn_backward(do, q, k, v, out, lse, None, True)
+    b = spa.flash_attn_backward(do, q, k, v, out, lse, None, True, deterministic=True)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    # ring-step form: fp32 dK/dV partials, non-causal, small grid (the query split would
+    # apply): deterministic=True must give identical bits on two runs
+    delta = la.bwd_delta(out, do)
+    res = []
+    for _ in range(2):
+        dq_acc = torch.empty(B, S, Hq, D, device="cuda")
+        dk = torch.empty(B, S, Hkv, D, device="cuda")
+        dv = torch.empty_like(dk)
+        la.attn_bwd_step(q, k, v, do, lse, delta, D ** -0.5, False, dq_acc, dk, dv,
+                         dq_overwrite=True, deterministic=True)
+        res.append((dq_acc, dk, dv))
+    spa.check_status()
+    for x, y in zip(*res):
+        assert torch.equal(x, y)
+
+
+def test_strided_lse_and_gradient_outputs(spa):
+    """lse/delta with a head stride (rows of a [B,Hq,2,h] tensor) and dq/dk/dv written
+    into head slices of one packed buffer give the same bits as contiguous tensors."""
+    from sp_aurora_b200 import local_attn as la
+    B, S, Hq, Hkv, D = 1, 512, 4, 2, 128
+    q, k, v, do = (_rand(sh, torch.bfloat16, s).cuda() for sh, s in (
+        ((B, S, Hq, D), 5), ((B, S, Hkv, D), 6), ((B, S, Hkv, D), 7), ((B, S, Hq, D), 8)))
+    out, lse = spa.flash_attn_forward(q, k, v, None, True)
+    want = spa.flash_attn_backward(do, q, k, v, out, lse, None, True)
+    wide = torch.empty(B, Hq, 2, S, device="cuda")
+    lse_v = wide[:, :, 1]
+    out2 = torch.empty_like(out)
+    la.attn_fwd_step(q, k, v, D ** -0.5, True, lse_v, out=out2)
+    assert torch.equal(out2, out) and torch.equal(lse_v, lse)
+    grads = torch.empty(B, S, Hq + 2 * Hkv, D, dtype=torch.bfloat16, device="cuda")
+    dq, dk, dv = grads[:, :, :Hq], grads[:, :, Hq:Hq + Hkv], grads[:, :, Hq + Hkv:]
+    delta = torch.empty(B, Hq, 2, S, device="cuda")
+    delta[:, :, 1] = la.bwd_delta(out, do)
+    la.attn_bwd_step(q, k, v, do, lse_v, delta[:, :, 1], D ** -0.5, True, None, dk, dv,
+                     dq=dq, dq_overwrite=True)
+    spa.check_status()
+    for got, ref in zip((dq, dk, dv), want):
+        assert torch.equal(got, ref)
 
 
 @pytest.mark.parametrize("B,Sq,Sk,Hq,Hkv,D,causal", TC_CASES[:4])
@@ -176,30 +243,6 @@ def test_large_shape_against_cuda_core_kernel(spa):
     ro, rl = orc.attention_ref(q[:, rows].cpu(), k.cpu(), v.cpu(), None, True, causal_off=3000)
     assert (out[:, rows].cpu().double() - ro).abs().max() <= 2e-2
     assert (lse[:, :, rows].cpu().double() - rl).abs().max() <= 1e-3
-
-
-def test_wide_tile_backward_variant_in_subprocess():
-    """The experimental 128x128-tile backward (SPA_BWD128=1, read once per process)
-    must give the same gradients as the default kernel."""
-    import subprocess
-    import sys
-    code = (
-        "import os, sys, torch; sys.path.insert(0, %r);"
-        "import sp_aurora_b200 as spa; from oracle import attention_oracle as orc;"
-        "g = torch.Generator().manual_seed(3);"
-        "q, k, v, do = (torch.randn(1, 384, 2, 128, generator=g).bfloat16() for _ in range(4));"
-        "ro, rl = orc.attention_ref(q, k, v, None, True);"
-        "r = orc.attention_bwd_ref(do, q, k, v, ro, rl, None, True);"
-        "out, lse = spa.flash_attn_forward(q.cuda(), k.cuda(), v.cuda(), None, True);"
-        "got = spa.flash_attn_backward(do.cuda(), q.cuda(), k.cuda(), v.cuda(), out, lse, None, True);"
-        "spa.check_status();"
-        "errs = [float((a.cpu().double() - b).abs().max()) for a, b in zip(got, r)];"
-        "lim = 2e-2 * max(1.0, float(r[2].abs().max()) / 4);"
-        "assert max(errs) <= lim, errs; print('ok', errs)"
-    ) % os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, SPA_BWD128="1")
-    res = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True, timeout=300)
-    assert res.returncode == 0, res.stdout + res.stderr
 
 
 _QSPLIT_CODE = r"""

@@ -117,9 +117,9 @@ def _zigzag_errs(rank, world, orc):
     """Balanced causal ring (internal zigzag re-layout) vs the full-sequence oracle."""
     from sp_aurora_b200 import zigzag
     errs = {}
-    for hq, hkv in ((4, 4), (4, 2)):
+    for hq, hkv, B in ((4, 4, 2), (4, 2, 2), (4, 2, 1)):   # batch 1 takes the merged-launch plan
         g = torch.Generator().manual_seed(21)
-        B, S, D = 2, 32 * world, 16
+        S, D = 32 * world, 16
         q = torch.randn(B, S, hq, D, generator=g)
         k = torch.randn(B, S, hkv, D, generator=g)
         v = torch.randn(B, S, hkv, D, generator=g)
@@ -134,7 +134,7 @@ def _zigzag_errs(rank, world, orc):
         dq, dk, dv = zigzag.zigzag_ring_backward(None, ds, *saved, D ** -0.5,
                                                  bwd_step=orc.bwd_step_cpu, delta_fn=orc.delta_cpu,
                                                  cast_fn=orc.cast_cpu)
-        errs[(hq, hkv)] = [
+        errs[(hq, hkv, B)] = [
             float((out.double() - full_out[:, sli]).abs().max()),
             float((lse.double() - full_lse[:, :, sli]).abs().max()),
             float((dq.double() - fdq[:, sli]).abs().max()),
@@ -276,6 +276,112 @@ def test_gloo_zigzag_ring_four_ranks():
         assert "error" not in res, res.get("error")
         for key, errs in res["zigzag_errs"].items():
             assert max(errs) < 2e-5, (r, key, errs)
+
+
+def test_zigzag_merged_plan_covers_the_same_blocks():
+    """The merged-launch plan (batch size 1) covers exactly the half-blocks of the
+    per-half plan, with the same masks."""
+    from sp_aurora_b200.zigzag import _plan, _step_calls
+    for W in (2, 4, 8):
+        for r in range(W):
+            for s in range(W):
+                want = sorted(_step_calls(s, r, W))
+                got = []
+                for q_lo, q_n, k_lo, k_n, causal, off in _plan(s, r, W, True):
+                    for qh in range(q_lo, q_lo + q_n):
+                        for kh in range(k_lo, k_lo + k_n):
+                            # causal call with offset `off` halves: half-block (qh-q_lo, kh-k_lo)
+                            # is diagonal when kh-k_lo == qh-q_lo+off, full when below it
+                            d = (kh - k_lo) - (qh - q_lo) - off
+                            assert not causal or d <= 0
+                            got.append((qh, kh, bool(causal and d == 0)))
+                assert sorted(got) == want, (W, r, s)
+                unmerged = sorted((c[0], c[2], c[4]) for c in _plan(s, r, W, False))
+                assert unmerged == want
+
+
+def test_attn_type_accepts_reference_and_yunchang_names():
+    """sp_aurora/ulysses/attn_layer.py:20-31: a str enum with these five values; every one
+    (and the yunchang spellings) must construct both hybrid modules."""
+    import sp_aurora_b200 as spa
+    ref = {"TORCH": "torch", "INTEL_SYCL": "intel_sycl", "INTEL_ONEDNN": "intel_onednn",
+           "FA": "flash_attn", "FA3": "flash_attn_3"}
+    assert {m.name: m.value for m in spa.AttnType} == ref
+    assert isinstance(spa.AttnType.FA, str) and spa.AttnType.FA == "flash_attn"
+    for value in list(ref.values()) + ["fa", "fa3", "sage_fp8", "sparse_sage"] + list(spa.AttnType):
+        spa.LongContextAttention(attn_type=value)
+        spa.LongContextAttentionQKVPacked(attn_type=value)
+        spa.UlyssesAttention(attn_type=value)
+        assert callable(spa.select_flash_attn_impl(value))
+    with pytest.raises(ValueError):
+        spa.LongContextAttention(attn_type="no_such_backend")
+
+
+def test_reference_export_names_exist():
+    """Names a caller of the reference imports from the package root
+    (sp_aurora/__init__.py:59-122, sp_aurora/intel_ring_flash_attn.py:453-456)."""
+    import sp_aurora_b200 as spa
+    for name in ("ring_flash_attn_func", "ring_flash_attn_kvpacked_func", "ring_flash_attn_qkvpacked_func",
+                 "ulysses_flash_attn_func", "ulysses_flash_attn_kvpacked_func",
+                 "ulysses_flash_attn_qkvpacked_func", "UlyssesComm", "SeqAllToAll4D", "SeqAllToAll5D",
+                 "UlyssesAttention", "PROCESS_GROUP", "set_seq_parallel_pg", "HAS_LONG_CTX_ATTN",
+                 "HAS_FLASH_ATTN", "HAS_SPARSE_SAGE_ATTENTION", "AttnType", "select_flash_attn_impl",
+                 "LongContextAttention", "RingFlashAttnFunc", "update_out_and_lse", "RingComm",
+                 "intel_ring_flash_attn_func", "intel_ring_flash_attn_kvpacked_func",
+                 "intel_ring_flash_attn_qkvpacked_func", "IntelRingFlashAttnFunc",
+                 "intel_ulysses_flash_attn_func", "sp_aurora_func", "sp_aurora_kvpacked_func",
+                 "sp_aurora_qkvpacked_func"):
+        assert hasattr(spa, name), name
+    comm = spa.UlyssesComm(None)
+    assert comm.world_size == 1 and comm.rank == 0
+    assert spa.HAS_SPARSE_SAGE_ATTENTION is False
+
+
+def test_misaligned_arguments_are_refused_before_any_launch():
+    """Vector loads need 16-byte aligned bases and strides: the C ABI answers
+    SPA_EINVAL instead of faulting (checked without a GPU: validation comes first)."""
+    import ctypes as C
+    from sp_aurora_b200 import _lib
+    lib = _lib.lib
+    buf = 0x10000                      # never dereferenced: the call is refused first
+    bad = buf + 2
+    H, D, S = 2, 64, 8
+    ss, sb = H * D, S * H * D
+    rc = lib.spa_bwd_delta(bad, sb, ss, D, buf, sb, ss, D, buf, 1, S, H, D, 1, None)
+    assert rc == -1 and b"16" in lib.spa_last_error()
+    rc = lib.spa_bwd_delta(buf, sb, ss + 1, D, buf, sb, ss, D, buf, 1, S, H, D, 1, None)
+    assert rc == -1
+    rc = lib.spa_cast_from_f32(buf, bad, sb, ss, D, 1, S, H, D, 1, C.c_float(1.0), None)
+    assert rc == -1
+    rc = lib.spa_merge(buf, buf, bad, sb, ss, D, buf, 1, S, H, D, 1, None)
+    assert rc == -1
+    a = _lib.FwdArgs()
+    a.q, a.k, a.v, a.out, a.lse = bad, buf, buf, buf, buf
+    for f in ("q", "k", "v", "o"):
+        setattr(a, f + "_sb", sb), setattr(a, f + "_ss", ss), setattr(a, f + "_sh", D)
+    a.B, a.Sq, a.Sk, a.Hq, a.Hkv, a.D, a.dtype, a.scale = 1, S, S, H, H, D, 1, 0.125
+    assert lib.spa_attn_fwd(C.byref(a)) == -1
+    b = _lib.BwdArgs()
+    b.q, b.k, b.v, b.dout, b.lse, b.delta, b.dq, b.dk, b.dv = buf, buf, buf, buf, buf, buf, buf, bad, buf
+    for f in ("q", "k", "v", "do"):
+        setattr(b, f + "_sb", sb), setattr(b, f + "_ss", ss), setattr(b, f + "_sh", D)
+    b.dq_overwrite = 1
+    b.B, b.Sq, b.Sk, b.Hq, b.Hkv, b.D, b.dtype, b.scale = 1, S, S, H, H, D, 1, 0.125
+    assert lib.spa_attn_bwd(C.byref(b)) == -1
+
+
+def test_shared_memory_attribute_cache_is_per_device():
+    """The opt-in shared-memory size is a per-device kernel attribute: the cache behind
+    it must treat (kernel, device) as the key."""
+    import ctypes as C
+    from sp_aurora_b200 import _lib
+    seen = _lib.lib.spa_internal_smem_attr_seen
+    seen.restype, seen.argtypes = C.c_int, [C.c_void_p, C.c_int, C.c_int]
+    k1, k2 = 0x1234000, 0x5678000
+    assert seen(k1, 0, 1000) == 0 and seen(k1, 0, 1000) == 1      # second time: cached
+    assert seen(k1, 1, 1000) == 0 and seen(k1, 1, 1000) == 1      # another device: not cached
+    assert seen(k2, 0, 1000) == 0
+    assert seen(k1, 0, 2000) == 0 and seen(k1, 0, 1500) == 1      # larger size: set again
 
 
 def test_zigzag_plan_is_balanced():
