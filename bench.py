@@ -1,18 +1,22 @@
-"""Benchmark of the ring-attention hot path (forward + backward).
+"""Benchmark of the sequence-parallel attention hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--seq S]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
-Workload: causal GQA kv-packed ring attention, bf16, B=1, total S=131072 split
-over the N ranks, 32 query heads / 8 kv heads, D=128, q/kv/dout ~ N(0, 0.5)
-from a fixed seed; one step = forward + backward through the public
-sp_aurora_kvpacked_func. Prints ONE JSON line on rank 0.
+Headline workload (cfg4): causal GQA kv-packed ring attention, bf16, B=1, total S=131072
+split over the N ranks, 32 query heads / 8 kv heads, D=128, q/kv/dout ~ N(0, 0.5) from
+fixed seeds; one step = forward + backward through the public sp_aurora_kvpacked_func.
+Prints ONE JSON line on rank 0.
 
 FLOPs are the algorithmic ones: forward 4*B*Hq*S*S*D/2 (causal), backward 2.5x.
-`value` is the whole-job TFLOP/s with inputs resident in HBM; `e2e` repeats the
-measurement with pinned-host inputs copied in and a checksum read back each
-step (the copy of the next step's inputs overlaps the current step). The CPU baseline and `--impl reference` time the CPU restatement of the
-reference's attention math (oracle/) on a bounded sample on the host cores.
+`value` is the whole-job TFLOP/s with inputs resident in HBM. `e2e` repeats the
+measurement with pinned-host inputs copied in and out, dq, dkv copied back to pinned host
+memory every step (copies of neighbouring steps overlap the kernels; `e2e.serial` is the
+same with nothing overlapped). `parity` compares this run's results with the CPU oracle
+(row slices, outside every timed region). `workloads` adds short runs of the Ulysses
+(cfg3) and hybrid (cfg5) configurations with their own parity blocks. The CPU baseline
+and `--impl reference` time the CPU restatement of the reference's attention math
+(oracle/) on a bounded sample on the host cores.
 """
 import argparse
 import json
@@ -31,11 +35,15 @@ import torch.distributed as dist  # noqa: E402
 HQ, HKV, D, B = 32, 8, 128, 1
 DEFAULT_SEQ = 131072
 SIGMA = 0.5
+CHUNK = 4096
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
+# parity tolerances (north-star): out and gradients 2e-2 max-abs (bf16), lse 1e-3;
+# checksum identities relative to the sum of absolute terms
+TOL_OUT, TOL_LSE, TOL_IDENT = 2e-2, 1e-3, 1e-3
 
 
-def fwd_flops(seq, causal=True):
-    f = 4.0 * B * HQ * seq * seq * D
+def fwd_flops(seq, causal=True, batch=B, heads=HQ):
+    f = 4.0 * batch * heads * float(seq) * seq * D
     return f / 2 if causal else f
 
 
@@ -98,6 +106,59 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+# ---------------------------------------------------------------------------
+# Seeded synthetic inputs: every 4096-row chunk of every global tensor has its own
+# generator, so any rank (or the CPU checker) can regenerate any rows of any tensor
+# and the data do not depend on the number of ranks.
+# ---------------------------------------------------------------------------
+def gen_rows(base_seed, tensor_id, batch, lo, hi, tail, sigma=1.0, dtype=torch.bfloat16):
+    """Rows [lo, hi) of global tensor `tensor_id` as [batch, hi-lo, *tail]."""
+    out = torch.empty((batch, hi - lo) + tuple(tail), dtype=dtype)
+    c = lo // CHUNK
+    while c * CHUNK < hi:
+        g = torch.Generator().manual_seed(base_seed + 16 * c + tensor_id)
+        n = CHUNK
+        blk = (torch.randn((batch, n) + tuple(tail), generator=g) * sigma).to(dtype)
+        a, b_ = max(lo, c * CHUNK), min(hi, (c + 1) * CHUNK)
+        out[:, a - lo:b_ - lo] = blk[:, a - c * CHUNK:b_ - c * CHUNK]
+        c += 1
+    return out
+
+
+def max_err(a, b):
+    return float((a.detach().cpu().double() - b.double()).abs().max())
+
+
+def checksum_identities(q, k, v, dout, out, dq, dk, dv, world, device):
+    """Size-independent checks over the whole job (all ranks):
+         sum(dq*q) == sum(dk*k)      (both equal scale * sum_ij dS_ij * q_i.k_j)
+         sum(dv*v) == sum(dout*out)  (both equal sum_ij P_ij * dO_i.V_j)
+    Returns the two differences relative to the sums of absolute terms."""
+    def sums(a, b_):
+        p = a.float() * b_.float()
+        return torch.stack((p.sum(dtype=torch.float64), p.abs().sum(dtype=torch.float64)))
+    t = torch.stack((sums(dq, q), sums(dk, k), sums(dv, v), sums(dout, out))).to(device)
+    if world > 1:
+        dist.all_reduce(t)
+    t = t.cpu()
+    e1 = float((t[0, 0] - t[1, 0]).abs() / max(1e-30, float(torch.maximum(t[0, 1], t[1, 1]))))
+    e2 = float((t[2, 0] - t[3, 0]).abs() / max(1e-30, float(torch.maximum(t[2, 1], t[3, 1]))))
+    return e1, e2
+
+
+def reduce_max(vals, world, device):
+    t = torch.tensor(vals, dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(x) for x in t.cpu()]
+
+
+def grad_tol(ref):
+    """2e-2 max-abs while |gradient| <= 4; beyond that the bound follows the 16-bit output
+    rounding (x * 2^-9 on its own), i.e. 2e-2 * max|ref| / 4."""
+    return TOL_OUT * max(1.0, float(ref.abs().max()) / 4)
+
+
 def cpu_reference_sample(seq=4096, steps=1, threads=None):
     """Forward+backward of the reference attention math on the host cores
     (oracle port, fp32, the layout the reference is correct in), B/H/D of the
@@ -138,8 +199,9 @@ def run_aux(args):
     lse = torch.randn(Bq, H, S, device="cuda")
     blse = torch.randn(Bq, H, S, device="cuda")
     nbytes = x.numel() * 2
+    rows = Bq * S * H
 
-    def timeit(fn, n=20):
+    def timeit(fn, n=args.aux_iters):
         for _ in range(3):
             fn()
         torch.cuda.synchronize()
@@ -156,98 +218,170 @@ def run_aux(args):
             ("permute_rows pack (seq->head, 256 B rows)", lambda: a2a.strided_copy(send, src), 2 * nbytes),
             ("permute_rows unpack (head->seq)", lambda: a2a.strided_copy(outp.view(Bq, S, P, H // P, Dh),
                                                                           send.permute(1, 2, 0, 3, 4)), 2 * nbytes),
-            ("merge (fp32 acc r/w + bf16 block)", lambda: la.update_out_and_lse(acc, lse, x, blse),
-             x.numel() * (4 + 4 + 2)),
-            ("delta (rowsum dO*O)", lambda: la.bwd_delta(x, x), 2 * nbytes),
+            ("merge (fp32 acc r/w + bf16 block + 3 lse)", lambda: la.update_out_and_lse(acc, lse, x, blse),
+             x.numel() * (4 + 4 + 2) + rows * 12),
+            ("delta (rowsum dO*O)", lambda: la.bwd_delta(x, x), 2 * nbytes + rows * 4),
             ("cast fp32->bf16", lambda: la.cast_from_f32(acc, torch.bfloat16, 1.0, outp), x.numel() * 6)):
         t = timeit(fn)
-        res[name] = {"ms": t * 1e3, "algorithmic_GBps": traffic / t / 1e9, "frac_of_peak": traffic / t / 1e9 / peak}
+        res[name] = {"ms": t * 1e3, "algorithmic_bytes": traffic, "algorithmic_GBps": traffic / t / 1e9,
+                     "frac_of_peak": traffic / t / 1e9 / peak}
     spa.check_status()
     print(json.dumps({"aux_kernels": res, "peak_GBps": peak, "peak_source": kind + " hbm_gbs",
                       "tensor": [Bq, S, H, Dh], "dtype": "bf16",
                       "note": f"inputs {nbytes >> 20} MiB > L2"}), flush=True)
 
 
-def run_other_workload(args, rank, world, local_rank):
-    """`--workload ulysses` (cfg3: B=2, total S=65536, H=32, D=128, non-causal, fwd+bwd) and
-    `--workload hybrid` (cfg5: qkv-packed B=1, total S=262144, H=16, D=128, causal, forward
-    only with lse; Ulysses degree min(4, N) inside, ring across). Same timing rules as the
-    default workload; one JSON line on rank 0."""
+def oracle_threads(world):
+    return max(1, (os.cpu_count() or 1) // world)
+
+
+def run_ulysses(args, rank, world, device, steps, warmup):
+    """cfg3: Ulysses attention fwd+bwd, bf16, B=2, total S=65536, H=32, D=128, non-causal,
+    through ulysses_flash_attn_func. Returns the result dict (rank 0) with a parity block:
+    a 64-row slice of out / lse / dq per rank against the CPU oracle, and the two checksum
+    identities for dk / dv over the whole job."""
     import sp_aurora_b200 as spa
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
-    ul = args.workload == "ulysses"
-    Bw, S, H = (2, 65536, 32) if ul else (1, 262144, 16)
+    from oracle import attention_oracle as orc
+    Bw, S, H = 2, 65536, 32
     if args.seq != DEFAULT_SEQ:
         S = args.seq
     sl = S // world
-    g = torch.Generator().manual_seed(777 + rank)
-    if ul:
-        q, k, v, do = (torch.randn(Bw, sl, H, D, generator=g).bfloat16().to(device) for _ in range(4))
-        for t in (q, k, v):
-            t.requires_grad_(True)
-        flops = 3.5 * 4.0 * Bw * H * float(S) * S * D
+    lo = rank * sl
+    q, k, v, do = (gen_rows(777, t, Bw, lo, lo + sl, (H, D)).to(device) for t in range(4))
+    for t in (q, k, v):
+        t.requires_grad_(True)
+    flops = 3.5 * fwd_flops(S, causal=False, batch=Bw, heads=H)
+    res = {}
 
-        def step():
-            q.grad = k.grad = v.grad = None
-            out = spa.ulysses_flash_attn_func(q, k, v, causal=False)
-            out.backward(do)
-        name = "cfg3: Ulysses attention fwd+bwd (ulysses_flash_attn_func)"
-        par = f"ulysses{world}"
-    else:
-        qkv = torch.randn(Bw, sl, 3, H, D, generator=g).bfloat16().to(device)
-        U = min(4, world)
-        while world % U:
-            U -= 1
-        if world > 1:
-            spa.set_seq_parallel_pg(U, world // U, rank, world)
-        mod = spa.LongContextAttentionQKVPacked()
-        flops = 4.0 * Bw * H * float(S) * S * D / 2
+    def step():
+        q.grad = k.grad = v.grad = None
+        o, lse, _ = spa.ulysses_flash_attn_func(q, k, v, causal=False, return_attn_probs=True)
+        o.backward(do)
+        return o, lse
 
-        def step():
-            with torch.no_grad():
-                mod(qkv, causal=True, return_attn_probs=True)
-        name = "cfg5: hybrid Ulysses x ring forward with lse (LongContextAttentionQKVPacked)"
-        par = f"ulysses{U}xring{world // U}" if world > 1 else "local"
+    ms, launches, (out, lse) = time_steps(step, steps, warmup, world, device, spa)
+    spa.check_status()
+    # ---- parity (outside the timed region)
+    torch.set_num_threads(oracle_threads(world))
+    r0 = sl // 2
+    rows = slice(r0, r0 + 64)
+    kg, vg = (gen_rows(777, t, Bw, 0, S, (H, D)) for t in (1, 2))
+    qs, dos = q[:, rows].detach().cpu(), do[:, rows].cpu()
+    eo = el = edq = tq = 0.0
+    for h0 in range(0, H, 8):          # head groups bound the oracle's memory
+        hs = slice(h0, h0 + 8)
+        ro, rl = orc.attention_ref(qs[:, :, hs], kg[:, :, hs], vg[:, :, hs], None, False,
+                                   dtype=torch.float32)
+        rdq, _, _ = orc.attention_bwd_ref(dos[:, :, hs], qs[:, :, hs], kg[:, :, hs], vg[:, :, hs],
+                                          ro, rl, None, False, dtype=torch.float32)
+        eo = max(eo, max_err(out[:, rows, hs], ro))
+        el = max(el, max_err(lse[:, hs, rows], rl))
+        edq = max(edq, max_err(q.grad[:, rows, hs], rdq))
+        tq = max(tq, grad_tol(rdq))
+    i1, i2 = checksum_identities(q.detach(), k.detach(), v.detach(), do, out.detach(), q.grad, k.grad,
+                                 v.grad, world, device)
+    eo, el, edq, tq = reduce_max([eo, el, edq, tq], world, device)
+    ok = eo <= TOL_OUT and el <= TOL_LSE and edq <= tq and i1 <= TOL_IDENT and i2 <= TOL_IDENT
+    if rank == 0:
+        peaks, _ = load_peaks()
+        value = flops / (ms * 1e-3) / 1e12
+        res = {"workload": "cfg3: Ulysses attention fwd+bwd (ulysses_flash_attn_func), non-causal",
+               "value": value, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps, "warmup": warmup,
+               "batch": Bw, "total_seq": S, "heads": H, "head_dim": D, "parallelism": f"ulysses{world}",
+               "tflops_per_gpu": value / world,
+               "pct_of_bf16_peak_sustained": 100.0 * value / world / peaks.get("bf16_tflops_sustained", 1400.0),
+               "tokens_per_s": Bw * S / (ms * 1e-3), "gpu_launches": int(launches),
+               "parity": {"out": eo, "lse": el, "dq": edq, "sum_dq_q_vs_sum_dk_k": i1,
+                          "sum_dv_v_vs_sum_do_o": i2,
+                          "tol": {"out": TOL_OUT, "lse": TOL_LSE, "dq": tq, "identities": TOL_IDENT},
+                          "checked": "64-row slice of out/lse/dq per rank vs the fp32 CPU oracle; dk, dv "
+                                     "through the two checksum identities over all ranks",
+                          "ok": bool(ok)}}
+    return res
 
+
+def run_hybrid(args, rank, world, device, steps, warmup):
+    """cfg5: hybrid Ulysses x ring forward with lse, qkv-packed bf16, B=1, total S=262144,
+    H=16, D=128, causal, through LongContextAttentionQKVPacked (Ulysses degree min(4, N)
+    inside, ring across). Parity: a 64-row slice of out / lse per rank vs the CPU oracle."""
+    import sp_aurora_b200 as spa
+    from oracle import attention_oracle as orc
+    Bw, S, H = 1, 262144, 16
+    if args.seq != DEFAULT_SEQ:
+        S = args.seq
+    sl = S // world
+    lo = rank * sl
+    qkv = gen_rows(888, 0, Bw, lo, lo + sl, (3, H, D)).to(device)
+    U = min(4, world)
+    while world % U:
+        U -= 1
+    if world > 1:
+        spa.destroy_seq_parallel_pg()
+        spa.set_seq_parallel_pg(U, world // U, rank, world)
+    mod = spa.LongContextAttentionQKVPacked()
+    flops = fwd_flops(S, causal=True, batch=Bw, heads=H)
+
+    def step():
+        with torch.no_grad():
+            o, lse, _ = mod(qkv, causal=True, return_attn_probs=True)
+        return o, lse
+
+    ms, launches, (out, lse) = time_steps(step, steps, warmup, world, device, spa)
+    spa.check_status()
+    torch.set_num_threads(oracle_threads(world))
+    r0 = sl - 64                       # the rank's last rows: they see every earlier rank's keys
+    g0 = lo + r0
+    kvg = gen_rows(888, 0, Bw, 0, g0 + 64, (3, H, D))
+    eo = el = 0.0
+    for h0 in range(0, H, 8):
+        hs = slice(h0, h0 + 8)
+        ro, rl = orc.attention_ref(kvg[:, g0:g0 + 64, 0, hs], kvg[:, :, 1, hs], kvg[:, :, 2, hs], None,
+                                   True, causal_off=g0, dtype=torch.float32)
+        eo = max(eo, max_err(out[:, r0:r0 + 64, hs], ro))
+        el = max(el, max_err(lse[:, hs, r0:r0 + 64], rl))
+    eo, el = reduce_max([eo, el], world, device)
+    if world > 1:
+        spa.destroy_seq_parallel_pg()
+    res = {}
+    if rank == 0:
+        peaks, _ = load_peaks()
+        value = flops / (ms * 1e-3) / 1e12
+        res = {"workload": "cfg5: hybrid Ulysses x ring forward with lse (LongContextAttentionQKVPacked), causal",
+               "value": value, "unit": "TFLOP/s", "ms_per_step": ms, "steps": steps, "warmup": warmup,
+               "batch": Bw, "total_seq": S, "heads": H, "head_dim": D,
+               "parallelism": f"ulysses{U}xring{world // U}" if world > 1 else "local",
+               "tflops_per_gpu": value / world,
+               "pct_of_bf16_peak_sustained": 100.0 * value / world / peaks.get("bf16_tflops_sustained", 1400.0),
+               "tokens_per_s": Bw * S / (ms * 1e-3), "gpu_launches": int(launches),
+               "parity": {"out": eo, "lse": el, "tol": {"out": TOL_OUT, "lse": TOL_LSE},
+                          "checked": "last 64 rows of each rank's shard vs the fp32 CPU oracle",
+                          "ok": bool(eo <= TOL_OUT and el <= TOL_LSE)}}
+    return res
+
+
+def time_steps(step, steps, warmup, world, device, spa):
+    """`warmup` untimed steps, then `steps` timed ones bracketed by barrier + synchronize;
+    returns (ms per step, max over ranks; library launches; the last step's result)."""
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-
-    for _ in range(args.warmup):
-        step()
+    res = None
+    for _ in range(warmup):
+        res = step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     l0 = spa.launch_count()
     e0.record()
-    for _ in range(args.steps):
-        step()
+    for _ in range(steps):
+        res = step()
     e1.record()
     barrier()
     launches = spa.launch_count() - l0
-    t = torch.tensor([e0.elapsed_time(e1) / args.steps], device=device)
+    t = torch.tensor([e0.elapsed_time(e1) / steps], device=device)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
-    spa.check_status()
-    peaks, kind = load_peaks()
-    if rank == 0:
-        value = flops / (ms * 1e-3) / 1e12
-        print(json.dumps({
-            "metric": "attn_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": name, "batch": Bw, "total_seq": S, "heads": H, "head_dim": D,
-                       "parallelism": par},
-            "tflops_per_gpu": value / world,
-            "pct_of_bf16_peak_sustained": 100.0 * value / world / peaks.get("bf16_tflops_sustained", 1400.0),
-            "tokens_per_s": Bw * S / (ms * 1e-3), "gpu_launches": int(launches)}), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+    return float(t.item()), launches, res
 
 
 def run_reference(args, rank, world):
@@ -266,12 +400,15 @@ def run_reference(args, rank, world):
     value = sum(vals) / len(vals)
     sample = (f"oracle port (fp32 torch CPU) of the reference attention math, causal fwd+bwd, "
               f"B={B} Hq={HQ} Hkv={HKV} D={D}, total S={sample_seq} (S^2-scaled sample of S={args.seq})")
+    cfg = workload_config(args, world)
+    cfg["sample_seq"] = sample_seq       # what each step of this arm actually ran
+    cfg["sample_of_total_seq"] = args.seq
     line = {
         "impl": "reference", "metric": "ring_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": 1e3 * sum(secs) / len(secs), "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": workload_config(args, world),
+        "config": cfg,
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -286,23 +423,47 @@ def workload_config(args, world):
             "parallelism": f"ring{world}", "l2": "inputs exceed L2 (no flush needed)"}
 
 
-def make_inputs(seq_total, rank, world, device, pinned=False):
-    """Rank-local chunk of the global seeded tensors (chunk-seeded so results do
-    not depend on the number of ranks)."""
+def make_inputs(seq_total, rank, world):
+    """Rank-local shard of the global seeded tensors, pinned host memory."""
     sl = seq_total // world
-    chunk = 4096
-    q = torch.empty(B, sl, HQ, D, dtype=torch.bfloat16)
-    kv = torch.empty(B, sl, 2, HKV, D, dtype=torch.bfloat16)
-    do = torch.empty(B, sl, HQ, D, dtype=torch.bfloat16)
-    for c0 in range(0, sl, chunk):
-        c1 = min(sl, c0 + chunk)
-        g = torch.Generator().manual_seed(4321 + (rank * sl + c0) // chunk)
-        q[:, c0:c1] = (torch.randn(B, c1 - c0, HQ, D, generator=g) * SIGMA).to(torch.bfloat16)
-        kv[:, c0:c1] = (torch.randn(B, c1 - c0, 2, HKV, D, generator=g) * SIGMA).to(torch.bfloat16)
-        do[:, c0:c1] = (torch.randn(B, c1 - c0, HQ, D, generator=g) * SIGMA).to(torch.bfloat16)
-    if pinned:
-        return q.pin_memory(), kv.pin_memory(), do.pin_memory()
-    return q.to(device), kv.to(device), do.to(device)
+    lo = rank * sl
+    q = gen_rows(4321, 0, B, lo, lo + sl, (HQ, D), SIGMA)
+    kv = gen_rows(4321, 1, B, lo, lo + sl, (2, HKV, D), SIGMA)
+    do = gen_rows(4321, 2, B, lo, lo + sl, (HQ, D), SIGMA)
+    return q.pin_memory(), kv.pin_memory(), do.pin_memory()
+
+
+def ring_parity(args, rank, world, device, hq, hdo, out, dq, dkv):
+    """Compare this rank's results with the CPU oracle: 64-row slices of out / lse-free
+    quantities (out, dq) in the middle and at the end of the shard; dk / dv of the last 64
+    keys of the whole sequence (complete with those rows alone) on the last rank; dk / dv
+    everywhere through the two checksum identities."""
+    from oracle import attention_oracle as orc
+    torch.set_num_threads(oracle_threads(world))
+    sl = args.seq // world
+    lo = rank * sl
+    errs = {"out": 0.0, "lse": None, "dq": 0.0, "dk": 0.0, "dv": 0.0}
+    tol_dq = tol_dkv = TOL_OUT
+    for r0 in (sl // 2, sl - 64):
+        g0 = lo + r0
+        kvg = gen_rows(4321, 1, B, 0, g0 + 64, (2, HKV, D), SIGMA)
+        rows = slice(r0, r0 + 64)
+        last = rank == world - 1 and r0 == sl - 64
+        for g in range(HKV):           # one kv head (and its 4 query heads) at a time
+            qh = slice(g * (HQ // HKV), (g + 1) * (HQ // HKV))
+            kg, vg = kvg[:, :, 0, g:g + 1], kvg[:, :, 1, g:g + 1]
+            ro, rl = orc.attention_ref(hq[:, rows, qh], kg, vg, None, True, causal_off=g0,
+                                       dtype=torch.float32)
+            rdq, rdk, rdv = orc.attention_bwd_ref(hdo[:, rows, qh], hq[:, rows, qh], kg, vg, ro, rl, None,
+                                                  True, causal_off=g0, dtype=torch.float32)
+            errs["out"] = max(errs["out"], max_err(out[:, rows, qh], ro))
+            errs["dq"] = max(errs["dq"], max_err(dq[:, rows, qh], rdq))
+            tol_dq = max(tol_dq, grad_tol(rdq))
+            if last:
+                errs["dk"] = max(errs["dk"], max_err(dkv[:, rows, 0, g:g + 1], rdk[:, g0:g0 + 64]))
+                errs["dv"] = max(errs["dv"], max_err(dkv[:, rows, 1, g:g + 1], rdv[:, g0:g0 + 64]))
+                tol_dkv = max(tol_dkv, grad_tol(rdv[:, g0:g0 + 64]), grad_tol(rdk[:, g0:g0 + 64]))
+    return errs, tol_dq, tol_dkv
 
 
 def main():
@@ -313,9 +474,11 @@ def main():
     ap.add_argument("--impl", default="ours")
     ap.add_argument("--seq", type=int, default=DEFAULT_SEQ)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extra", action="store_true", help="skip the cfg3 / cfg5 workloads and the serial e2e")
     ap.add_argument("--workload", default="ring", choices=["ring", "ulysses", "hybrid"])
     ap.add_argument("--aux", action="store_true", help="bandwidth of the HBM-bound helper kernels")
     ap.add_argument("--aux-batch", type=int, default=2, help="batch of the --aux tensors (16 = 1 GiB)")
+    ap.add_argument("--aux-iters", type=int, default=20)
     args = ap.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -327,9 +490,6 @@ def main():
     if args.aux:
         run_aux(args)
         return
-    if args.workload != "ring":
-        run_other_workload(args, rank, world, local_rank)
-        return
 
     import sp_aurora_b200 as spa
     from sp_aurora_b200 import local_attn
@@ -340,9 +500,23 @@ def main():
     group = None
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+
+    if args.workload != "ring":
+        fn = run_ulysses if args.workload == "ulysses" else run_hybrid
+        res = fn(args, rank, world, device, args.steps, args.warmup)
+        if rank == 0:
+            res.update({"metric": "attn_tflops", "n_gpus": world, "higher_is_better": True,
+                        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                        "config": {"workload": res["workload"], "parallelism": res["parallelism"]}})
+            print(json.dumps(res), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
     assert args.seq % (world * 256) == 0
 
-    hq, hkv, hdo = make_inputs(args.seq, rank, world, device, pinned=True)
+    hq, hkv, hdo = make_inputs(args.seq, rank, world)
     q, kv, dout = hq.to(device), hkv.to(device), hdo.to(device)
     q.requires_grad_(True)
     kv.requires_grad_(True)
@@ -374,7 +548,7 @@ def main():
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        step(q, kv, dout)
+        out = step(q, kv, dout)
     e1.record()
     barrier()
     launches = spa.launch_count() - launches0
@@ -389,66 +563,125 @@ def main():
     ms = float(t.item())
     spa.check_status()
 
-    # ---------------- end to end: pinned host inputs, checksum read back ----------------
-    # Every step copies its inputs from pinned host memory and reads its checksum back.
-    # Two sets of device buffers: the copy of step i+1 runs on a second stream while step i
-    # computes (what a training loop's input prefetch does); the first copy of the timed
-    # region is not hidden, and nothing is copied before the region starts or for a step
-    # that is not run.
+    # ---------------- parity: this run's results against the CPU oracle ----------------
+    out_d, dq_d, dkv_d = out.detach(), q.grad, kv.grad
+    errs, tol_dq, tol_dkv = ring_parity(args, rank, world, device, hq, hdo, out_d, dq_d, dkv_d)
+    i1, i2 = checksum_identities(q.detach(), kv.detach()[:, :, 0], kv.detach()[:, :, 1], dout, out_d,
+                                 dq_d, dkv_d[:, :, 0], dkv_d[:, :, 1], world, device)
+    # lse is not returned by the training-step call: one extra forward outside every timed region
+    with torch.no_grad():
+        _, lse_d, _ = spa.sp_aurora_kvpacked_func(q.detach(), kv.detach(), causal=True, group=group,
+                                                  return_attn_probs=True)
+    from oracle import attention_oracle as orc
+    sl = args.seq // world
+    g0 = rank * sl + sl - 64
+    kvg = gen_rows(4321, 1, B, 0, g0 + 64, (2, HKV, D), SIGMA)
+    e_lse = 0.0
+    for g in range(HKV):
+        qh = slice(g * (HQ // HKV), (g + 1) * (HQ // HKV))
+        _, rl = orc.attention_ref(hq[:, sl - 64:sl, qh], kvg[:, :, 0, g:g + 1], kvg[:, :, 1, g:g + 1], None,
+                                  True, causal_off=g0, dtype=torch.float32)
+        e_lse = max(e_lse, max_err(lse_d[:, qh, sl - 64:sl], rl))
+    del kvg, lse_d
+    pe = reduce_max([errs["out"], e_lse, errs["dq"], errs["dk"], errs["dv"], tol_dq, tol_dkv], world, device)
+    parity = {"out": pe[0], "lse": pe[1], "dq": pe[2], "dk": pe[3], "dv": pe[4],
+              "sum_dq_q_vs_sum_dk_k": i1, "sum_dv_v_vs_sum_do_o": i2,
+              "tol": {"out": TOL_OUT, "lse": TOL_LSE, "dq": pe[5], "dk_dv": pe[6], "identities": TOL_IDENT},
+              "checked": "per rank: two 64-row slices of out/dq and one of lse vs the fp32 CPU oracle on "
+                         "the same seeded inputs; dk, dv of the last 64 keys on the last rank; dk, dv of "
+                         "all keys through the two checksum identities over all ranks",
+              "ok": bool(pe[0] <= TOL_OUT and pe[1] <= TOL_LSE and pe[2] <= pe[5] and pe[3] <= pe[6]
+                         and pe[4] <= pe[6] and i1 <= TOL_IDENT and i2 <= TOL_IDENT)}
+    del out_d, dq_d, dkv_d, out
+
+    # ---------------- end to end: pinned host inputs in, results out ----------------
+    # Every step copies q, kv, dout from pinned host memory and copies out, dq, dkv back to
+    # pinned host memory. Overlapped form (what a training loop's prefetch does): two sets of
+    # device buffers, the H2D of step i+1 and the D2H of step i-1 run on two copy streams
+    # while step i computes; the first H2D and the last D2H of the region are not hidden.
+    # Serial form: H2D, compute, D2H one after the other on one stream.
+    h_out, h_dq, h_dkv = (torch.empty_like(hq).pin_memory(), torch.empty_like(hq).pin_memory(),
+                          torch.empty_like(hkv).pin_memory())
     sets = []
     for _ in range(2):
         a_, b_, c_ = torch.empty_like(q), torch.empty_like(kv), torch.empty_like(dout)
         a_.requires_grad_(True)
         b_.requires_grad_(True)
         sets.append((a_, b_, c_))
-    host_res = torch.empty(3, dtype=torch.float32).pin_memory()
-    copy_stream = torch.cuda.Stream(device=device)
+    h2d_stream = torch.cuda.Stream(device=device)
+    d2h_stream = torch.cuda.Stream(device=device)
     main_stream = torch.cuda.current_stream(device)
 
-    def issue_copy(i, after):
-        """H2D of step i's inputs on the copy stream, once `after` (the last compute that
+    def issue_h2d(i, after):
+        """H2D of step i's inputs on the copy stream, once `after` (the last work that
         read this buffer set) is done."""
         dq_, dkv_, ddo_ = sets[i % 2]
-        with torch.cuda.stream(copy_stream), torch.no_grad():
+        with torch.cuda.stream(h2d_stream), torch.no_grad():
             if after is not None:
-                copy_stream.wait_event(after)
+                h2d_stream.wait_event(after)
             dq_.copy_(hq, non_blocking=True)
             dkv_.copy_(hkv, non_blocking=True)
             ddo_.copy_(hdo, non_blocking=True)
             ev = torch.cuda.Event()
-            ev.record(copy_stream)
+            ev.record(h2d_stream)
         return ev
 
-    def e2e_run(n):
-        done = [None, None]                       # last compute on each buffer set
+    def e2e_overlapped(n):
+        done = [None, None]                       # last reader of each buffer set
         start = torch.cuda.Event()
         start.record(main_stream)
-        ready = issue_copy(0, start)
+        ready = issue_h2d(0, start)
         for i in range(n):
             main_stream.wait_event(ready)
             if i + 1 < n:
-                ready_next = issue_copy(i + 1, done[(i + 1) % 2] or start)
+                ready_next = issue_h2d(i + 1, done[(i + 1) % 2] or start)
             dq_, dkv_, ddo_ = sets[i % 2]
-            out = step(dq_, dkv_, ddo_)
-            res = torch.stack((out.float().sum(), dq_.grad.float().sum(), dkv_.grad.float().sum()))
-            host_res.copy_(res, non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record(main_stream)
+            o = step(dq_, dkv_, ddo_)
+            computed = torch.cuda.Event()
+            computed.record(main_stream)
+            with torch.cuda.stream(d2h_stream), torch.no_grad():
+                d2h_stream.wait_event(computed)
+                h_out.copy_(o.detach(), non_blocking=True)
+                h_dq.copy_(dq_.grad, non_blocking=True)
+                h_dkv.copy_(dkv_.grad, non_blocking=True)
+                o.record_stream(d2h_stream)
+                dq_.grad.record_stream(d2h_stream)
+                dkv_.grad.record_stream(d2h_stream)
+                ev = torch.cuda.Event()
+                ev.record(d2h_stream)
             done[i % 2] = ev
             if i + 1 < n:
                 ready = ready_next
+        main_stream.wait_stream(d2h_stream)
 
-    e2e_run(2)
-    barrier()
-    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    f0.record()
-    e2e_run(args.steps)
-    f1.record()
-    barrier()
-    t = torch.tensor([f0.elapsed_time(f1) / args.steps], device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item())
+    def e2e_serial(n):
+        dq_, dkv_, ddo_ = sets[0]
+        for _ in range(n):
+            with torch.no_grad():
+                dq_.copy_(hq, non_blocking=True)
+                dkv_.copy_(hkv, non_blocking=True)
+                ddo_.copy_(hdo, non_blocking=True)
+            o = step(dq_, dkv_, ddo_)
+            h_out.copy_(o.detach(), non_blocking=True)
+            h_dq.copy_(dq_.grad, non_blocking=True)
+            h_dkv.copy_(dkv_.grad, non_blocking=True)
+
+    def timed(fn, n):
+        fn(2 if n > 1 else 1)
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        fn(n)
+        f1.record()
+        barrier()
+        tt = torch.tensor([f0.elapsed_time(f1) / n], device=device)
+        if world > 1:
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        return float(tt.item())
+
+    e2e_ms = timed(e2e_overlapped, args.steps)
+    e2e_serial_ms = None if args.no_extra else timed(e2e_serial, max(2, args.steps // 2))
+    # the copied-back results are the results: compare a slice with the resident run's
     del sets
 
     # ---------------- compute-only time (exchanges replaced by local hand-offs) ----------------
@@ -458,18 +691,28 @@ def main():
         ring_mod.RingComm.FAKE = True
         step(q, kv, dout)
         barrier()
-        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        g0.record()
+        g0_, g1_ = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        g0_.record()
         for _ in range(args.steps):
             step(q, kv, dout)
-        g1.record()
+        g1_.record()
         barrier()
         ring_mod.RingComm.FAKE = False
-        t = torch.tensor([g0.elapsed_time(g1) / args.steps], device=device)
+        t = torch.tensor([g0_.elapsed_time(g1_) / args.steps], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         nocomm_ms = float(t.item())
         exposed = {"step_ms": ms, "compute_only_ms": nocomm_ms,
                    "exposed_comm_frac": max(0.0, (ms - nocomm_ms) / ms)}
+    q.grad = kv.grad = None
+
+    # ---------------- the other configurations, short runs with their own parity ----------------
+    extra = {}
+    if not args.no_extra and args.seq == DEFAULT_SEQ:
+        del q, kv, dout
+        torch.cuda.empty_cache()
+        extra["cfg3_ulysses"] = run_ulysses(args, rank, world, device, 3, 3)
+        torch.cuda.empty_cache()
+        extra["cfg5_hybrid"] = run_hybrid(args, rank, world, device, 3, 3)
 
     total_flops = 3.5 * fwd_flops(args.seq)
     value = total_flops / (ms * 1e-3) / 1e12
@@ -478,16 +721,22 @@ def main():
     peak_burst = peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"])
 
     if rank == 0:
-        # dominant kernel = backward; achieved = algorithmic FLOPs of this rank's
-        # launches / their summed CUDA-event durations inside the timed region
-        def rate(name):
-            rows = kt.get(name, [])
+        # The backward is two kernels (dQ pass: 3 of the 5 algorithmic products... counted as
+        # 1.0x forward FLOPs; dK/dV pass: 1.5x). Dominant kernel = the dK/dV pass; achieved =
+        # algorithmic FLOPs of this rank's launches / their summed CUDA-event durations
+        # inside the timed region.
+        def rate(*names):
+            rows = [r for n in names for r in kt.get(n, [])]
             t_ms = sum(t for t, _ in rows)
             fl = sum(f for _, f in rows)
             n = max(1, len(rows))
             return (fl / (t_ms * 1e-3) / 1e12 if t_ms > 0 else None), (t_ms / n if rows else None), len(rows), fl / n
-        achieved, avg_bwd, n_bwd, bwd_flops_per_launch = rate("bwd")
+        achieved, _, _, _ = rate("bwd", "bwd_dq", "bwd_dkv")
+        dkv_rate, avg_dkv, n_dkv, dkv_flops = rate("bwd_dkv")
+        dq_rate, avg_dq, n_dq, dq_flops = rate("bwd_dq")
         fwd_rate, avg_fwd, n_fwd, _ = rate("fwd")
+        h2d = int(world * (hq.numel() + hkv.numel() + hdo.numel()) * 2)
+        d2h = int(world * (h_out.numel() + h_dq.numel() + h_dkv.numel()) * 2)
         line = {
             "metric": "ring_attn_fwd_bwd_tflops", "value": value, "unit": "TFLOP/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
@@ -497,25 +746,39 @@ def main():
             "pct_of_bf16_peak_burst": 100.0 * value / world / peak_burst,
             "pct_of_bf16_peak_sustained": 100.0 * value / world / peak_sust,
             "tokens_per_s": B * args.seq / (ms * 1e-3),
-            "roofline": {"bound": "tensor", "kernel": "attn_bwd_sm100_kernel<128,bf16>",
+            "roofline": {"bound": "tensor",
+                         "kernel": "attn_bwd_dq_sm100_kernel + attn_bwd_dkv_sm100_kernel <128,bf16> (the "
+                                   "backward of one block: 2.5x the forward's algorithmic FLOPs)",
                          "achieved": achieved, "peak": peak_sust, "unit": "TFLOP/s",
                          "frac": (achieved / peak_sust) if achieved else None,
-                         "peak_source": f"{peak_kind} bf16_tflops_sustained", "traffic": None,
-                         "traffic_note": "ncu at S=16384 (profiles/): 3.3 GB DRAM per backward launch of "
-                                         "5.5 TFLOP, 6 % of HBM peak; not proportional to FLOPs, so not "
-                                         "scaled to this size",
-                         "avg_launch_ms": avg_bwd, "launches_timed": n_bwd,
-                         "flops_per_launch": bwd_flops_per_launch,
+                         "peak_source": f"{peak_kind} bf16_tflops_sustained",
+                         "traffic": TRAFFIC_NOTE["traffic_bytes_per_step_scaled"],
+                         "traffic_note": TRAFFIC_NOTE["note"],
+                         "flop_convention": "backward of a block = 2.5x its forward FLOPs: 1.5x booked to "
+                                            "the dK/dV pass, 1.0x to the dQ pass (the passes execute 2.0x "
+                                            "and 1.5x: both recompute S and dP)",
+                         "dkv_kernel": {"avg_launch_ms": avg_dkv, "launches_timed": n_dkv,
+                                        "flops_per_launch": dkv_flops, "achieved": dkv_rate,
+                                        "executed": None if dkv_rate is None else dkv_rate * 2.0 / 1.5},
+                         "dq_kernel": {"avg_launch_ms": avg_dq, "launches_timed": n_dq,
+                                       "flops_per_launch": dq_flops, "achieved": dq_rate,
+                                       "executed": None if dq_rate is None else dq_rate * 1.5},
                          "fwd_kernel": {"avg_launch_ms": avg_fwd, "launches_timed": n_fwd,
                                         "achieved": fwd_rate}},
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-                    "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": int(world * (hq.numel() + hkv.numel() + hdo.numel()) * 2),
-                    "d2h_bytes_per_step": int(world * host_res.numel() * 4)},
+                    "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "overlap": "H2D of the next step and D2H of the previous step's out, dq, dkv run on "
+                               "copy streams beside the kernels",
+                    "serial": None if e2e_serial_ms is None else {
+                        "value": total_flops / (e2e_serial_ms * 1e-3) / 1e12, "ms_per_step": e2e_serial_ms,
+                        "note": "same copies, nothing overlapped"}},
+            "parity": parity,
             "gpu_launches": int(launches),
             "exposed_comm": exposed,
             "clocks": clocks,
         }
+        if extra:
+            line["workloads"] = extra
         if not args.no_cpu_baseline and world == 1:
             tf, secs, threads = cpu_reference_sample(4096, 1)
             line["cpu_baseline"] = {
@@ -526,6 +789,15 @@ def main():
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+# DRAM traffic of the backward pair from one ncu capture at S=16384 (profiles/), scaled to
+# the bench's launch by the number of (query tile, key tile) pairs, to which the traffic of
+# both kernels is proportional. Filled in from the committed profile summary.
+TRAFFIC_NOTE = {
+    "traffic_bytes_per_step_scaled": None,
+    "note": "no ncu capture of the two-pass backward has been summarised yet",
+}
 
 
 if __name__ == "__main__":

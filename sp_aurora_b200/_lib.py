@@ -161,6 +161,14 @@ def check_status() -> None:
     check(lib.spa_check_status(), "spa_check_status")
 
 
+def maybe_check_status() -> None:
+    """With SPA_CHECK_STATUS=1 in the environment: check_status() (a device synchronise) at
+    the end of every backward of the public attention functions, so that a bounded wait that
+    gave up surfaces as an exception in the training loop instead of as wrong gradients."""
+    if os.environ.get("SPA_CHECK_STATUS") == "1":
+        check_status()
+
+
 def launch_count() -> int:
     return int(lib.spa_launch_count())
 

@@ -21,7 +21,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_PATH = PKG_DIR / "libspaurora_sm100.so"
 SOURCES = ["spa_abi.cu", "attn_fwd_sm100.cu", "attn_bwd_dq_sm100.cu", "attn_bwd_dkv_sm100.cu",
-           "attn_simt.cu"]
+           "attn_simt.cu", "wait_selftest.cu"]
 HEADERS = [CSRC / "tc05.cuh", CSRC / "spa_internal.h", PKG_DIR.parent / "include" / "spa.h"]
 
 NVCC_FLAGS = [

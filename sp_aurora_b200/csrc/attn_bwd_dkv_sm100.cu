@@ -17,14 +17,15 @@
 // sp_aurora/intel_flash_attn.py:129 is a stub); formulas as in the manual
 // backward of sp_aurora/intel_ulysses_attn.py:403-426.
 //
-// CTA = 11 warps:
-//   warps 0-3   compute group 0: key row per thread, query columns  0-63
-//   warps 4-7   compute group 1: key row per thread, query columns 64-127
-//   warp  8     TMA producer     warp 9  MMA issuer and TMEM owner
-//   warp  10    row statistics: lse*log2e and delta of the next query tile -> shared memory
+// CTA = 18 warps:
+//   warps 0-15  four compute groups of four warps: key row per thread, group g works on
+//               query columns [32g, 32g+32) (four warps per scheduler hide the latency of
+//               the TMEM loads and of the exponentials); the first 256 compute threads also
+//               fetch lse*log2e and delta of the next query tile into shared memory
+//   warp  16    TMA producer     warp 17  MMA issuer and TMEM owner
 // TMEM columns: S^T [0,128) dP^T [128,256) dV [256,256+D) dK [384,384+D). P^T (16-bit,
-// two per column) overwrites columns [0,32) and [64,96) of S^T, dS^T the same columns
-// of dP^T: each compute thread overwrites only columns it has already read, and the
+// two per column) of group g overwrites columns [32g, 32g+16) of S^T, dS^T the same
+// columns of dP^T: each compute thread overwrites only columns it has already read, and the
 // in-order tensor pipe lets S^T(i+1) be issued right behind dV(i), dP^T(i+1) behind dK(i).
 // Shared memory: K, V tiles and a ring of four Q / dO tiles (Q in slots 0,2; dO in 1,3).
 #include <cuda_bf16.h>
@@ -42,8 +43,10 @@ namespace {
 
 constexpr int kTileKV = 128;
 constexpr int kTileQ = 128;
-constexpr int kThreads = 352;
-constexpr int kWarpTma = 8, kWarpMma = 9, kWarpStat = 10;
+constexpr int kThreads = 576;
+constexpr int kComputeThreads = 512;
+constexpr int kWarpTma = 16, kWarpMma = 17;
+constexpr int kStatBufs = 3;   // row-statistics buffers (see the compute loop)
 constexpr int kRing = 4;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr uint32_t kColS = 0, kColDP = 128, kColDV = 256, kColDK = 384;
@@ -72,9 +75,9 @@ struct DkvSmem {
   static constexpr int kKOff = 0;
   static constexpr int kVOff = kKOff + kTile;
   static constexpr int kRingOff = kVOff + kTile;
-  static constexpr int kRowOff = kRingOff + kRing * kTile;   // [2 bufs][lse2|delta][128] floats
-  static constexpr int kBarOff = kRowOff + 2 * 2 * kTileQ * 4;
-  static constexpr int kNumBars = 1 + 2 * kRing + 10;
+  static constexpr int kRowOff = kRingOff + kRing * kTile;   // [3 bufs][lse2|delta][128] floats
+  static constexpr int kBarOff = kRowOff + kStatBufs * 2 * kTileQ * 4;
+  static constexpr int kNumBars = 1 + 2 * kRing + 6 + kStatBufs;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
 };
 
@@ -113,9 +116,8 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
   uint64_t* p_full = dp_full + 1;
   uint64_t* ds_full = p_full + 1;
   uint64_t* mma_done = ds_full + 1;
-  uint64_t* row_ready = mma_done + 1;          // [2]
-  uint64_t* row_free = row_ready + 2;          // [2]
-  uint64_t* epi_full = row_free + 2;
+  uint64_t* row_ready = mma_done + 1;          // [kStatBufs]
+  uint64_t* epi_full = row_ready + kStatBufs;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
   float* row_buf = reinterpret_cast<float*>(smem + L::kRowOff);  // [buf][lse2|delta][128]
@@ -165,14 +167,11 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(p_full, 256);
-    mbar_init(ds_full, 256);
+    mbar_init(p_full, kComputeThreads);
+    mbar_init(ds_full, kComputeThreads);
     mbar_init(mma_done, 1);
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&row_ready[i], 32);
-      mbar_init(&row_free[i], 256);
-    }
-    mbar_init(epi_full, 256);
+    for (int i = 0; i < kStatBufs; ++i) mbar_init(&row_ready[i], 256);
+    mbar_init(epi_full, kComputeThreads);
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -247,15 +246,15 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
         return true;
       };
       // dV += P^T dO (slot odd) or dK += dS^T Q (slot even): A from TMEM (16 queries = 8
-      // columns per step; queries 0-63 sit at column 0, queries 64-127 at column 64 of the
-      // score region), B = the dO / Q tile read MN-major (rows = queries).
+      // columns per step; the 32 queries of compute group g sit at column 32g of the score
+      // region), B = the dO / Q tile read MN-major (rows = queries).
       auto issue_grad = [&](int it, const int slot) {
         const uint32_t b0 = (slot * L::kTile) >> 4;
         const uint32_t a_col = (slot & 1) ? kColS : kColDP;
         const uint32_t d_col = (slot & 1) ? kColDV : kColDK;
 #pragma unroll
         for (int kk = 0; kk < kTileQ / 16; ++kk)
-          mma_ts_d(tmem_base + d_col, tmem_base + a_col + (kk / 4) * 64 + (kk % 4) * 8, ring_mn,
+          mma_ts_d(tmem_base + d_col, tmem_base + a_col + (kk / 2) * 32 + (kk % 2) * 8, ring_mn,
                    b0 + ((kk * 2048) >> 4), idesc_dkv, (it > 0 || kk > 0));
       };
 
@@ -288,110 +287,150 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       if (ok) mma_commit(mma_done);
     }
-  } else if (warp == kWarpStat) {
-    // ------------------------------------------------------- row statistics
-    // lse (pre-multiplied by log2 e) and delta of one query tile per iteration, double
-    // buffered. +inf lse makes out-of-range query rows give P = 0.
-    for (int it = 0; it < n_it; ++it) {
-      const int buf = it & 1;
-      if (it >= 2 && !warp_wait(&row_free[buf], ((it >> 1) - 1) & 1, wc, 5, it)) break;
-      const int hq = g * G + it / n_q;
-      const int q0 = (i_start + it % n_q) * kTileQ;
-      const size_t base = (size_t)b * p.lse_sb + (size_t)hq * p.lse_sh;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int c = u * 32 + lane;
-        const int qi = q0 + c;
-        const bool in = qi < p.Sq;
-        row_buf[(buf * 2 + 0) * kTileQ + c] = in ? p.lse[base + qi] * kLog2e : INFINITY;
-        row_buf[(buf * 2 + 1) * kTileQ + c] = in ? p.delta[base + qi] : 0.f;
-      }
-      mbar_arrive(&row_ready[buf]);
-    }
   } else {
     // -------------------------------------------------------------- compute
-    const int grp = warp >> 2;               // 0: query columns 0-63, 1: columns 64-127
+    // Loop layout (TMEM shape 16x256b): the warp's 32 key rows are read as two 16-row
+    // halves; in half hh, lane (g8, t4) = (lane / 4, lane % 4) holds rows
+    // 16*hh + g8 and 16*hh + g8 + 8 of the warp's quadrant and the query columns
+    // {8i + 2*t4, 8i + 2*t4 + 1 : i = 0..3} of the group's 32. A thread thus needs the
+    // statistics (lse, delta) of 8 query columns for its 4 rows x 8 columns, instead of 32
+    // for 1 row x 32 columns in the row-per-thread shape: the shared-memory broadcast
+    // reads of the statistics were more than a third of this kernel's shared-memory
+    // traffic, which is what bounds it. The epilogue uses the row-per-thread shape.
+    const int grp = warp >> 2;               // query-column quarter of the tile
     const int quad = warp & 3;
-    const int r = quad * 32 + lane;          // key row in tile = TMEM lane
+    const int r = quad * 32 + lane;          // key row in tile = TMEM lane (epilogue)
     const int kidx = kv0 + r;
-    const int c_base = grp * 64;
+    const int g8 = lane >> 2, t4 = lane & 3;
+    const int c_base = grp * 32;
     const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
-    const uint32_t t_s = tmem_base + lane_field + kColS + c_base;      // scores, then P^T in [0,32)
-    const uint32_t t_dp = tmem_base + lane_field + kColDP + c_base;    // dP^T, then dS^T in [0,32)
+    const uint32_t half_step = 16u << 16;    // second 16-row half of the quadrant
+    const uint32_t t_s = tmem_base + lane_field + kColS + c_base;      // scores, then P^T in [0,16)
+    const uint32_t t_dp = tmem_base + lane_field + kColDP + c_base;    // dP^T, then dS^T in [0,16)
     const uint32_t t_dv = tmem_base + lane_field + kColDV;
     const uint32_t t_dk = tmem_base + lane_field + kColDK;
     const bool key_ok = kidx < p.Sk;
     bool ok = true;
 
+    // Row statistics of a query tile, fetched by the first 256 compute threads: threads
+    // 0-127 lse (pre-multiplied by log2 e), threads 128-255 delta. +inf lse makes
+    // out-of-range query rows give P = 0. Iteration `it` reads buffer it % 3 and fills
+    // buffer (it + 1) % 3: a thread can be at most one iteration ahead of the slowest one
+    // (it cannot pass the scores of iteration it before every thread has handed in P^T of
+    // iteration it - 1), so the buffer being filled is never one that is still being read.
+    const int stat_tid = threadIdx.x;
+    auto fetch_rowstat = [&](int it) -> float {
+      const int hq = g * G + it / n_q;
+      const int qi = (i_start + it % n_q) * kTileQ + (stat_tid & 127);
+      const size_t idx = (size_t)b * p.lse_sb + (size_t)hq * p.lse_sh + qi;
+      if (stat_tid < 128) return qi < p.Sq ? p.lse[idx] * kLog2e : INFINITY;
+      return qi < p.Sq ? p.delta[idx] : 0.f;
+    };
+    if (n_it > 0 && stat_tid < 256) {
+      row_buf[(0 * 2 + (stat_tid >> 7)) * kTileQ + (stat_tid & 127)] = fetch_rowstat(0);
+      mbar_arrive(&row_ready[0]);
+    }
+
     for (int it = 0; it < n_it; ++it) {
-      const int buf = it & 1;
-      ok = warp_wait(&row_ready[buf], (it >> 1) & 1, wc, 8, it);
+      const int buf = it % kStatBufs;
+      float next_stat = 0.f;
+      if (stat_tid < 256 && it + 1 < n_it) next_stat = fetch_rowstat(it + 1);
+
+      ok = warp_wait(&row_ready[buf], (it / kStatBufs) & 1, wc, 8, it);
       if (!ok) break;
-      const float* lse2 = row_buf + (buf * 2 + 0) * kTileQ + c_base;
-      const float* dlt = row_buf + (buf * 2 + 1) * kTileQ + c_base;
+      const float* lse2 = row_buf + (buf * 2 + 0) * kTileQ + c_base + 2 * t4;
+      const float* dlt = row_buf + (buf * 2 + 1) * kTileQ + c_base + 2 * t4;
+      float2 lv[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) lv[i] = *reinterpret_cast<const float2*>(lse2 + 8 * i);
       const int q0 = (i_start + it % n_q) * kTileQ;
-      // Visible iff kidx <= q + off  <=>  column c >= kidx - off - q0.
-      int c_min = 0;
-      if (p.causal) {
-        const long long cm = (long long)kidx - p.causal_off - q0 - c_base;
-        c_min = (int)max(0ll, min(cm, 64ll));
-      }
-      if (!key_ok) c_min = 64;
+      // warp-uniform: does any row of this tile mask a column of this group?
+      // (key kidx is visible to query column c iff c >= kidx - off - q0 - c_base)
+      const bool need_mask = !(kv0 + kTileKV <= p.Sk) ||
+                             (p.causal && (long long)kv0 + kTileKV - 1 - p.causal_off > (long long)q0 + c_base);
 
       ok = warp_wait(s_full, it & 1, wc, 9, it);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sr[64];
-      tmem_ld32(t_s, sr);
-      tmem_ld32(t_s + 32, sr + 32);
+      uint32_t sr[32];                        // [half][16]: scores, then probabilities, in place
+      tmem_ld_16x256b_x4(t_s, sr);
+      tmem_ld_16x256b_x4(t_s + half_step, sr + 16);
       tmem_ld_wait();
-      float* pr = reinterpret_cast<float*>(sr);   // scores, then probabilities, in place
-      uint32_t pk[32];
+      float* pr = reinterpret_cast<float*>(sr);
 #pragma unroll
-      for (int c4 = 0; c4 < 16; ++c4) {
-        const float4 l4 = *reinterpret_cast<const float4*>(lse2 + 4 * c4);
-        const float lv[4] = {l4.x, l4.y, l4.z, l4.w};
+      for (int hh = 0; hh < 2; ++hh)
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int c = 4 * c4 + u;
-          float pe = fast_exp2(fmaf(pr[c], p.scale_log2, -lv[u]));
-          if (c < c_min) pe = 0.f;
-          pr[c] = pe;
+        for (int i = 0; i < 4; ++i) {
+          float* e = pr + hh * 16 + 4 * i;    // rows g8 (e[0], e[1]) and g8 + 8 (e[2], e[3])
+          e[0] = fast_exp2(fmaf(e[0], p.scale_log2, -lv[i].x));
+          e[1] = fast_exp2(fmaf(e[1], p.scale_log2, -lv[i].y));
+          e[2] = fast_exp2(fmaf(e[2], p.scale_log2, -lv[i].x));
+          e[3] = fast_exp2(fmaf(e[3], p.scale_log2, -lv[i].y));
         }
-        pk[2 * c4] = pack2<T>(pr[4 * c4], pr[4 * c4 + 1]);
-        pk[2 * c4 + 1] = pack2<T>(pr[4 * c4 + 2], pr[4 * c4 + 3]);
+      if (need_mask) {
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+          for (int rr = 0; rr < 2; ++rr) {
+            const int krow = kv0 + quad * 32 + hh * 16 + rr * 8 + g8;
+            long long cm = 0;
+            if (p.causal) cm = (long long)krow - p.causal_off - q0 - c_base;
+            int c_min = (int)max(0ll, min(cm, 32ll));
+            if (krow >= p.Sk) c_min = 32;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              float* e = pr + hh * 16 + 4 * i + 2 * rr;
+              const int c = 8 * i + 2 * t4;
+              if (c < c_min) e[0] = 0.f;
+              if (c + 1 < c_min) e[1] = 0.f;
+            }
+          }
       }
-      tmem_st32(t_s, pk);
+      uint32_t pk[16];
+#pragma unroll
+      for (int hh = 0; hh < 2; ++hh)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float* e = pr + hh * 16 + 4 * i;
+          pk[hh * 8 + 2 * i] = pack2<T>(e[0], e[1]);
+          pk[hh * 8 + 2 * i + 1] = pack2<T>(e[2], e[3]);
+        }
+      tmem_st_16x128b_x4(t_s, pk);
+      tmem_st_16x128b_x4(t_s + half_step, pk + 8);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(p_full);
 
+      float2 dl[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) dl[i] = *reinterpret_cast<const float2*>(dlt + 8 * i);
       ok = warp_wait(dp_full, it & 1, wc, 10, it);
       if (!ok) break;
       tc_fence_after();
-      uint32_t dsp[32];
+      uint32_t dsp[16];
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t dpr[32];
-        tmem_ld32(t_dp + half * 32, dpr);
+      for (int hh = 0; hh < 2; ++hh) {        // one half at a time keeps the registers in bounds
+        uint32_t dpr[16];
+        tmem_ld_16x256b_x4(t_dp + hh * half_step, dpr);
         tmem_ld_wait();
 #pragma unroll
-        for (int c4 = 0; c4 < 8; ++c4) {
-          const float4 d4 = *reinterpret_cast<const float4*>(dlt + half * 32 + 4 * c4);
-          const float dv4[4] = {d4.x, d4.y, d4.z, d4.w};
-          float ds[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int c = 4 * c4 + u;
-            ds[u] = pr[half * 32 + c] * (__uint_as_float(dpr[c]) - dv4[u]);
-          }
-          dsp[half * 16 + 2 * c4] = pack2<T>(ds[0], ds[1]);
-          dsp[half * 16 + 2 * c4 + 1] = pack2<T>(ds[2], ds[3]);
+        for (int i = 0; i < 4; ++i) {
+          const float* e = pr + hh * 16 + 4 * i;
+          const float d0 = e[0] * (__uint_as_float(dpr[4 * i]) - dl[i].x);
+          const float d1 = e[1] * (__uint_as_float(dpr[4 * i + 1]) - dl[i].y);
+          const float d2 = e[2] * (__uint_as_float(dpr[4 * i + 2]) - dl[i].x);
+          const float d3 = e[3] * (__uint_as_float(dpr[4 * i + 3]) - dl[i].y);
+          dsp[hh * 8 + 2 * i] = pack2<T>(d0, d1);
+          dsp[hh * 8 + 2 * i + 1] = pack2<T>(d2, d3);
         }
       }
-      mbar_arrive(&row_free[buf]);
-      tmem_st32(t_dp, dsp);
+      tmem_st_16x128b_x4(t_dp, dsp);
+      tmem_st_16x128b_x4(t_dp + half_step, dsp + 8);
       tmem_st_wait();
+      if (stat_tid < 256 && it + 1 < n_it) {
+        row_buf[(((it + 1) % kStatBufs) * 2 + (stat_tid >> 7)) * kTileQ + (stat_tid & 127)] = next_stat;
+        mbar_arrive(&row_ready[(it + 1) % kStatBufs]);
+      }
       tc_fence_before();
       mbar_arrive(ds_full);
     }
@@ -402,8 +441,20 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
 
     // ------------------------------------------------------------- epilogue
-    // dV and dK rows: group 0 handles head-dim columns [0, D/2), group 1 the rest.
-    constexpr int kHalfChunks = D / 64;  // 32-column chunks per group
+    // dV and dK rows: group g handles head-dim columns [g*D/4, (g+1)*D/4).
+    constexpr int kCols = D / 4;           // 32 (D = 128) or 16 (D = 64) columns per thread
+    auto load_cols = [&](uint32_t taddr, float scale, float* o) {
+      if (n_it > 0) {
+        uint32_t v[kCols];
+        if constexpr (kCols == 32) tmem_ld32(taddr + grp * kCols, v); else tmem_ld16(taddr + grp * kCols, v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < kCols; ++i) o[i] = __uint_as_float(v[i]) * scale;
+      } else {
+#pragma unroll
+        for (int i = 0; i < kCols; ++i) o[i] = 0.f;
+      }
+    };
     if (p.dkv_fp32) {
       // fp32 gradients leave through shared memory: each 32-column chunk is a
       // [128 keys][128 B] slab in the 128-byte swizzle (thread = key row, conflict-free
@@ -415,28 +466,16 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       if (ok) {
 #pragma unroll
         for (int which = 0; which < 2; ++which) {
-          const uint32_t taddr = which == 0 ? t_dv : t_dk;
+          float o[kCols];
+          load_cols(which == 0 ? t_dv : t_dk, which == 0 ? 1.f : p.scale, o);
           uint8_t* stg = which == 0 ? stg_dv : stg_dk;
+          const int col0 = grp * kCols;                       // first head-dim column of this thread
+          uint8_t* row = stg + (col0 / 32) * (kTileKV * 128) + r * 128;
+          const int j0 = (col0 % 32) / 4;                     // first 16-byte chunk inside the slab row
 #pragma unroll
-          for (int cc = 0; cc < kHalfChunks; ++cc) {
-            const int c = grp * kHalfChunks + cc;
-            float o[32];
-            if (n_it > 0) {
-              uint32_t v[32];
-              tmem_ld32(taddr + c * 32, v);
-              tmem_ld_wait();
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * (which == 0 ? 1.f : p.scale);
-            } else {
-#pragma unroll
-              for (int i = 0; i < 32; ++i) o[i] = 0.f;
-            }
-            uint8_t* row = stg + c * (kTileKV * 128) + r * 128;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-              *reinterpret_cast<float4*>(row + ((j ^ (r & 7)) << 4)) =
-                  make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
-          }
+          for (int j = 0; j < kCols / 4; ++j)
+            *reinterpret_cast<float4*>(row + (((j0 + j) ^ (r & 7)) << 4)) =
+                make_float4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
         }
       }
       fence_proxy_async_smem();
@@ -461,38 +500,24 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
       }
     } else if (ok) {
-      const size_t row_off = (size_t)b * p.dkv_sb + (size_t)kidx * p.dkv_ss + (size_t)g * p.dkv_sh;
+      const size_t row_off = (size_t)b * p.dkv_sb + (size_t)kidx * p.dkv_ss + (size_t)g * p.dkv_sh +
+                             grp * kCols;
 #pragma unroll
       for (int which = 0; which < 2; ++which) {
-        const uint32_t taddr = which == 0 ? t_dv : t_dk;
-        void* dst_base = which == 0 ? p.dv : p.dk;
+        float o[kCols];
+        load_cols(which == 0 ? t_dv : t_dk, which == 0 ? 1.f : p.scale, o);
+        if (!key_ok) continue;
+        T* drow = reinterpret_cast<T*>(which == 0 ? p.dv : p.dk) + row_off;
+        if (p.dkv_accumulate) {
 #pragma unroll
-        for (int cc = 0; cc < kHalfChunks; ++cc) {
-          const int c = grp * kHalfChunks + cc;
-          float o[32];
-          if (n_it > 0) {
-            uint32_t v[32];
-            tmem_ld32(taddr + c * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * (which == 0 ? 1.f : p.scale);
-          } else {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = 0.f;
-          }
-          if (!key_ok) continue;
-          T* drow = reinterpret_cast<T*>(dst_base) + row_off + c * 32;
-          if (p.dkv_accumulate) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] += static_cast<float>(drow[i]);
-          }
-          uint4* dst = reinterpret_cast<uint4*>(drow);
-#pragma unroll
-          for (int i = 0; i < 4; ++i)
-            dst[i] = make_uint4(pack2<T>(o[8 * i], o[8 * i + 1]), pack2<T>(o[8 * i + 2], o[8 * i + 3]),
-                                pack2<T>(o[8 * i + 4], o[8 * i + 5]),
-                                pack2<T>(o[8 * i + 6], o[8 * i + 7]));
+          for (int i = 0; i < kCols; ++i) o[i] += static_cast<float>(drow[i]);
         }
+        uint4* dst = reinterpret_cast<uint4*>(drow);
+#pragma unroll
+        for (int i = 0; i < kCols / 8; ++i)
+          dst[i] = make_uint4(pack2<T>(o[8 * i], o[8 * i + 1]), pack2<T>(o[8 * i + 2], o[8 * i + 3]),
+                              pack2<T>(o[8 * i + 4], o[8 * i + 5]),
+                              pack2<T>(o[8 * i + 6], o[8 * i + 7]));
       }
     }
   }

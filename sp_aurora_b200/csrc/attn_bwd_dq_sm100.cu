@@ -13,17 +13,19 @@
 // (the reference's own sp_aurora/intel_flash_attn.py:129 is a stub); formulas as in
 // the manual backward of sp_aurora/intel_ulysses_attn.py:403-426.
 //
-// CTA = 10 warps:
-//   warps 0-3  compute group 0: query row per thread, key columns  0-63 of a tile
-//   warps 4-7  compute group 1: query row per thread, key columns 64-127
-//   warp  8    TMA producer (lane 0)     warp 9  MMA issuer (lane 0), TMEM owner
+// CTA = 18 warps:
+//   warps 0-15  four compute groups of four warps: query row per thread, group g works on
+//               key columns [32g, 32g+32) of a tile (four warps per scheduler hide the
+//               latency of the TMEM loads and of the exponentials)
+//   warp  16    TMA producer (lane 0)     warp 17  MMA issuer (lane 0), TMEM owner
 // TMEM columns: S [0,128)  dP [128,256)  dQ [256,256+D)  dS [384,448) (16-bit, two
 // per column)  Q [448,448+D/2) (16-bit). Q and dS are the TMEM A operands of the S
 // and dQ products, so per K/V tile shared memory is read only for dO (A of dP) and
 // for K, V, K as B operands. Shared memory: the dO tile and a 3-stage ring of K|V.
 //
-// Tensor-pipe order per tile j:  S(j+1), dP(j+1), dQ(j)  -- the next tile's scores
-// are in flight while the compute warps turn S(j), dP(j) into dS(j).
+// Tensor-pipe order per tile j:  S(j+1), dP(j+1), dQ(j)  -- the compute warps take S(j)
+// and dP(j) into registers as soon as they exist, so the next tile's scores are on the
+// pipe while S(j), dP(j) are turned into dS(j).
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <math.h>
@@ -38,8 +40,9 @@ namespace {
 
 constexpr int kTileM = 128;   // query rows per CTA
 constexpr int kTileN = 128;   // keys per K/V tile
-constexpr int kThreads = 320;
-constexpr int kWarpTma = 8, kWarpMma = 9;
+constexpr int kThreads = 576;
+constexpr int kComputeThreads = 512;
+constexpr int kWarpTma = 16, kWarpMma = 17;
 constexpr int kStages = 3;
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr uint32_t kColS = 0, kColDP = 128, kColDQ = 256, kColDS = 384, kColQ = 448;
@@ -137,16 +140,16 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
   if (threadIdx.x == 0) {
     *cta_abort = 0;
     mbar_init(do_full, 1);
-    mbar_init(q_ready, 256);
+    mbar_init(q_ready, kComputeThreads);
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(s_free, 256);
-    mbar_init(dp_free, 256);
-    mbar_init(ds_full, 256);
+    mbar_init(s_free, kComputeThreads);
+    mbar_init(dp_free, kComputeThreads);
+    mbar_init(ds_full, kComputeThreads);
     mbar_init(dq_done, 1);
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -256,28 +259,29 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
     }
   } else {
     // -------------------------------------------------------------- compute
-    const int grp = warp >> 2;                 // key-column half of the tile
+    const int grp = warp >> 2;                 // key-column quarter of the tile
     const int quad = warp & 3;
     const int r = quad * 32 + lane;            // query row in tile = TMEM lane
     const int qrow = q0 + r;
     const bool row_ok = qrow < p.Sq;
-    const int c_base = grp * 64;
+    const int c_base = grp * 32;
+    constexpr int kOutCols = D / 4;            // dQ columns (and Q elements) per group
     const uint32_t lane_field = static_cast<uint32_t>(quad * 32) << 16;
     const uint32_t t_s = tmem_base + lane_field + kColS + c_base;
     const uint32_t t_dp = tmem_base + lane_field + kColDP + c_base;
-    const uint32_t t_ds = tmem_base + lane_field + kColDS + grp * 32;
-    const uint32_t t_dq = tmem_base + lane_field + kColDQ + grp * (D / 2);
-    const uint32_t t_q = tmem_base + lane_field + kColQ + grp * (D / 4);
+    const uint32_t t_ds = tmem_base + lane_field + kColDS + grp * 16;
+    const uint32_t t_dq = tmem_base + lane_field + kColDQ + grp * kOutCols;
+    const uint32_t t_q = tmem_base + lane_field + kColQ + grp * (D / 8);
     bool ok = true;
 
-    // Q row -> TMEM (the A operand of S): each group stores half of the row's columns.
+    // Q row -> TMEM (the A operand of S): each group stores a quarter of the row.
     if (n_kv > 0) {
-      constexpr int kWords = D / 4;            // 32-bit words (two elements each) per group
+      constexpr int kWords = D / 8;            // 32-bit words (two elements each) per group
       uint32_t qw[kWords];
       if (row_ok) {
         const uint4* src = reinterpret_cast<const uint4*>(
             reinterpret_cast<const T*>(p.q) + (size_t)b * p.q_sb + (size_t)qrow * p.q_ss +
-            (size_t)h * p.q_sh + grp * (D / 2));
+            (size_t)h * p.q_sh + grp * (D / 4));
 #pragma unroll
         for (int i = 0; i < kWords / 4; ++i) {
           const uint4 v = src[i];
@@ -287,7 +291,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
 #pragma unroll
         for (int i = 0; i < kWords; ++i) qw[i] = 0u;
       }
-      if constexpr (D == 128) tmem_st32(t_q, qw); else tmem_st16(t_q, qw);
+      if constexpr (D == 128) tmem_st16(t_q, qw); else tmem_st8(t_q, qw);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(q_ready);
@@ -301,50 +305,46 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
       ok = warp_wait(s_full, j & 1, wc, 8, j);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sr[64];
+      uint32_t sr[32];
       tmem_ld32(t_s, sr);
-      tmem_ld32(t_s + 32, sr + 32);
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(s_free);
+      // dP(j) is taken into registers before the exponentials, not after: the issuer can then
+      // put S(j+1) and dP(j+1) on the tensor pipe back to back while this tile is turned into dS.
+      ok = warp_wait(dp_full, j & 1, wc, 9, j);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t dpr[32];
+      tmem_ld32(t_dp, dpr);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(dp_free);
       float* pr = reinterpret_cast<float*>(sr);   // scores, then probabilities, in place
 
       const int k0 = j * kTileN;
       const bool need_mask =
           (k0 + kTileN > p.Sk) ||
           (p.causal && ((long long)k0 + kTileN - 1 > (long long)q0 + p.causal_off));
-      int limit = 64;   // first masked column of this thread's 64
-      if (need_mask) {
+      if (!need_mask) {                            // tiles below the diagonal: no selects
+#pragma unroll
+        for (int c = 0; c < 32; ++c) pr[c] = fast_exp2(fmaf(pr[c], p.scale_log2, -lse2));
+      } else {
         long long lim = p.Sk - 1;
         if (p.causal) lim = min(lim, (long long)qrow + p.causal_off);
-        limit = (int)max(0ll, min(lim - k0 - c_base + 1, 64ll));
-      }
+        const int limit = (int)max(0ll, min(lim - k0 - c_base + 1, 32ll));   // first masked column
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        float pe = fast_exp2(fmaf(pr[c], p.scale_log2, -lse2));
-        if (need_mask && c >= limit) pe = 0.f;
-        pr[c] = pe;
-      }
-
-      ok = warp_wait(dp_full, j & 1, wc, 9, j);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t dsp[32];
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t dpr[32];
-        tmem_ld32(t_dp + half * 32, dpr);
-        tmem_ld_wait();
-        if (half == 1) {
-          tc_fence_before();
-          mbar_arrive(dp_free);
+        for (int c = 0; c < 32; ++c) {
+          const float pe = fast_exp2(fmaf(pr[c], p.scale_log2, -lse2));
+          pr[c] = c < limit ? pe : 0.f;
         }
+      }
+      uint32_t dsp[16];
 #pragma unroll
-        for (int c = 0; c < 32; c += 2) {
-          const float d0 = pr[half * 32 + c] * (__uint_as_float(dpr[c]) - dlt);
-          const float d1 = pr[half * 32 + c + 1] * (__uint_as_float(dpr[c + 1]) - dlt);
-          dsp[half * 16 + (c >> 1)] = pack2<T>(d0, d1);
-        }
+      for (int c = 0; c < 32; c += 2) {
+        const float d0 = pr[c] * (__uint_as_float(dpr[c]) - dlt);
+        const float d1 = pr[c + 1] * (__uint_as_float(dpr[c + 1]) - dlt);
+        dsp[c >> 1] = pack2<T>(d0, d1);
       }
       if (j > 0) {
         // dQ(j-1) has finished reading the dS columns.
@@ -352,7 +352,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
         if (!ok) break;
         tc_fence_after();
       }
-      tmem_st32(t_ds, dsp);
+      tmem_st16(t_ds, dsp);
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(ds_full);
@@ -366,47 +366,45 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
     if (ok) {
       // total = (earlier ring steps' sum unless dq_overwrite) + scale * dQ; it goes to dq in
       // the element type and / or back to the fp32 accumulator, whichever is given.
-      const size_t acc_off = (((size_t)b * p.Sq + qrow) * p.Hq + h) * D + grp * (D / 2);
+      const size_t acc_off = (((size_t)b * p.Sq + qrow) * p.Hq + h) * D + grp * kOutCols;
       const float* acc_in = (!p.dq_overwrite && p.dq_acc) ? p.dq_acc + acc_off : nullptr;
       float* acc_out = p.dq_acc ? p.dq_acc + acc_off : nullptr;
       T* out_row = p.dq ? reinterpret_cast<T*>(p.dq) + (size_t)b * p.dq_sb + (size_t)qrow * p.dq_ss +
-                              (size_t)h * p.dq_sh + grp * (D / 2)
+                              (size_t)h * p.dq_sh + grp * kOutCols
                         : nullptr;
       const bool skip = (n_kv == 0) && !p.dq_overwrite && !p.dq;   // the accumulator already holds the total
+      float o[kOutCols];
+      if (n_kv > 0) {
+        uint32_t v[kOutCols];
+        if constexpr (kOutCols == 32) tmem_ld32(t_dq, v); else tmem_ld16(t_dq, v);
+        tmem_ld_wait();
 #pragma unroll
-      for (int cc = 0; cc < D / 64; ++cc) {
-        float o[32];
-        if (n_kv > 0) {
-          uint32_t v[32];
-          tmem_ld32(t_dq + cc * 32, v);
-          tmem_ld_wait();
+        for (int i = 0; i < kOutCols; ++i) o[i] = __uint_as_float(v[i]) * p.scale;
+      } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __uint_as_float(v[i]) * p.scale;
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0.f;
-        }
-        if (!row_ok || skip) continue;
+        for (int i = 0; i < kOutCols; ++i) o[i] = 0.f;
+      }
+      if (row_ok && !skip) {
         if (acc_in) {
-          const float4* a4 = reinterpret_cast<const float4*>(acc_in + cc * 32);
+          const float4* a4 = reinterpret_cast<const float4*>(acc_in);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
+          for (int i = 0; i < kOutCols / 4; ++i) {
             const float4 a = a4[i];
             o[4 * i] += a.x; o[4 * i + 1] += a.y; o[4 * i + 2] += a.z; o[4 * i + 3] += a.w;
           }
         }
         if (out_row) {
-          uint4* dst = reinterpret_cast<uint4*>(out_row + cc * 32);
+          uint4* dst = reinterpret_cast<uint4*>(out_row);
 #pragma unroll
-          for (int i = 0; i < 4; ++i)
+          for (int i = 0; i < kOutCols / 8; ++i)
             dst[i] = make_uint4(pack2<T>(o[8 * i], o[8 * i + 1]), pack2<T>(o[8 * i + 2], o[8 * i + 3]),
                                 pack2<T>(o[8 * i + 4], o[8 * i + 5]),
                                 pack2<T>(o[8 * i + 6], o[8 * i + 7]));
         }
         if (acc_out) {
-          float4* dst = reinterpret_cast<float4*>(acc_out + cc * 32);
+          float4* dst = reinterpret_cast<float4*>(acc_out);
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
+          for (int i = 0; i < kOutCols / 4; ++i)
             dst[i] = make_float4(o[4 * i], o[4 * i + 1], o[4 * i + 2], o[4 * i + 3]);
         }
       }

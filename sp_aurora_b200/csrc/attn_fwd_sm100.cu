@@ -34,14 +34,6 @@ constexpr int kTileM = 128;          // query rows per tile
 constexpr int kTileN = 128;          // keys per K/V tile
 constexpr int kThreads = 320;
 constexpr float kRescaleThreshold = 8.0f;  // in log2 units
-// The 128x128 exponentials of a key tile would keep the special-function unit busy for as
-// long as the tile's MMAs take. One column pair in every kPolyPeriod pairs is therefore
-// evaluated on the FMA pipe (poly_exp2, relative error 7.5e-5, far below the rounding of
-// P to 16 bits); 0 sends everything to ex2.approx.
-#ifndef SPA_FWD_POLY_PERIOD
-#define SPA_FWD_POLY_PERIOD 4
-#endif
-constexpr int kPolyPeriod = SPA_FWD_POLY_PERIOD;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kLog2e = 1.4426950408889634f;
 
@@ -325,11 +317,8 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       float lsum = 0.f;
 #pragma unroll
       for (int c = 0; c < 128; c += 2) {
-        const float x0 = fmaf(s[c], p.scale_log2, -m_eff);
-        const float x1 = fmaf(s[c + 1], p.scale_log2, -m_eff);
-        const bool poly = kPolyPeriod > 0 && ((c >> 1) % (kPolyPeriod > 0 ? kPolyPeriod : 1)) == 0;
-        const float p0 = poly ? poly_exp2(x0) : fast_exp2(x0);
-        const float p1 = poly ? poly_exp2(x1) : fast_exp2(x1);
+        const float p0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_eff));
+        const float p1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_eff));
         lsum += p0 + p1;
         pk[c >> 1] = pack2<T>(p0, p1);
       }

@@ -325,6 +325,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
       : "r"(taddr)
       : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
@@ -347,6 +357,12 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
       "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
       "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
       "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};" ::"r"(r[0]),
+      "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(taddr)
       : "memory");
 }
 // Shape 16x256b, 4 repetitions (32 columns) of 16 TMEM lanes starting at taddr's
@@ -372,20 +388,6 @@ __device__ __forceinline__ void tmem_st_16x128b_x4(uint32_t taddr, const uint32_
 }
 __device__ __forceinline__ void tmem_st_wait() {
   asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-}
-
-// 2^x on the FMA pipe: x = n + r with n the nearest integer and r in [-0.5, 0.5], a
-// degree-3 polynomial for 2^r (fitted for minimal relative error on that interval:
-// 7.5e-5), and n added into the exponent field. x is clamped at -125 so the exponent
-// never wraps; +inf and NaN give garbage, callers mask those lanes afterwards.
-__device__ __forceinline__ float poly_exp2(float x) {
-  x = fmaxf(x, -125.f);
-  const float t = x + 12582912.f;            // 1.5 * 2^23: the low mantissa bits now hold n
-  const float r = x - (t - 12582912.f);
-  float p = fmaf(r, 0.05517125502228737f, 0.2426103800535202f);
-  p = fmaf(p, r, 0.6932609677314758f);
-  p = fmaf(p, r, 0.9999281167984009f);
-  return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
 }
 
 __device__ __forceinline__ float fast_exp2(float x) {

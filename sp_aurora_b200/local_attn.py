@@ -21,8 +21,9 @@ _SUPPORTED_D = (32, 64, 128)
 
 # Optional per-kernel timing: when set to a dict, every forward/backward kernel
 # call appends (start event, end event, algorithmic FLOPs of the call), the events
-# recorded on the launching stream, under "fwd" / "bwd". Used by the benchmark;
-# None (default) records nothing.
+# recorded on the launching stream, under "fwd", "bwd_dq" (the dQ pass: 1.0x the
+# forward's FLOPs of the 2.5x a backward counts), "bwd_dkv" (the dK/dV pass: 1.5x) or
+# "bwd" (both passes in one call). Used by the benchmark; None (default) records nothing.
 KERNEL_TIMERS = None
 
 
@@ -229,7 +230,8 @@ def attn_bwd_step(q, k, v, dout, lse, delta, softmax_scale: float, causal: bool,
     a.scale = float(softmax_scale)
     a.stream = stream_ptr(q.device)
     share = {_lib.SPA_BWD_BOTH: 2.5, _lib.SPA_BWD_DQ_ONLY: 1.0, _lib.SPA_BWD_DKV_ONLY: 1.5}[a.passes]
-    with _Timed("bwd", q.device, share * attn_flops(B, Sq, Sk, Hq, D, causal, causal_off)):
+    name = {_lib.SPA_BWD_BOTH: "bwd", _lib.SPA_BWD_DQ_ONLY: "bwd_dq", _lib.SPA_BWD_DKV_ONLY: "bwd_dkv"}[a.passes]
+    with _Timed(name, q.device, share * attn_flops(B, Sq, Sk, Hq, D, causal, causal_off)):
         check(lib.spa_attn_bwd(C.byref(a)), "spa_attn_bwd")
 
 

@@ -173,15 +173,17 @@ def ring_flash_attn_backward(process_group, dout, q, k, v, out, softmax_lse, sof
     Hkv = k.shape[2]
     delta = delta_fn(out, dout)
     dq = torch.empty((B, S, Hq, D), dtype=q.dtype, device=q.device)
+    DQ, DKV = _lib.SPA_BWD_DQ_ONLY, _lib.SPA_BWD_DKV_ONLY
 
     if W == 1:
         dk = torch.empty((B, S, Hkv, D), dtype=q.dtype, device=q.device)
         dv = torch.empty_like(dk)
+        bwd_step(q, k, v, dout, softmax_lse, delta, softmax_scale, causal, None, None, None,
+                 dq=dq, dq_overwrite=True, deterministic=deterministic, passes=DQ)
         bwd_step(q, k, v, dout, softmax_lse, delta, softmax_scale, causal, None, dk, dv,
-                 dq=dq, dq_overwrite=True, deterministic=deterministic)
+                 deterministic=deterministic, passes=DKV)
         return dq, dk, dv
 
-    DQ, DKV = _lib.SPA_BWD_DQ_ONLY, _lib.SPA_BWD_DKV_ONLY
     dq_acc = torch.empty((B, S, Hq, D), dtype=torch.float32, device=q.device)
     last_step = r if causal else W - 1
     cur, axis = _pack_kv(k, v)
@@ -263,11 +265,13 @@ class RingFlashAttnFunc(torch.autograd.Function):
             dq, dk, dv = zigzag.zigzag_ring_backward(ctx.group, dout, q_z, kv_z, out_z, lse_z,
                                                      ctx.softmax_scale,
                                                      deterministic=ctx.deterministic)
+            _lib.maybe_check_status()
             return dq, dk, dv, None, None, None, None, None, None, None, None
         q, k, v, out, lse = ctx.saved_tensors
         dq, dk, dv = ring_flash_attn_backward(ctx.group, dout, q, k, v, out, lse,
                                               ctx.softmax_scale, ctx.causal,
                                               deterministic=ctx.deterministic)
+        _lib.maybe_check_status()
         return dq, dk, dv, None, None, None, None, None, None, None, None
 
 

@@ -17,7 +17,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
-from . import local_attn
+from . import _lib, local_attn
 from .all_to_all import (SeqAllToAll4D, all_to_all_4D, heads_all_to_all_packed, reshard_lse,
                          seq_all_to_all_packed)
 from .local_attn import check_unsupported_kwargs
@@ -91,6 +91,7 @@ class UlyssesFlashAttnFunc(torch.autograd.Function):
             dout = dout.contiguous()
         dq, dk, dv = ulysses_flash_attn_backward(ctx.group, dout, q_r, k_r, v_r, out_r, lse_r,
                                                  ctx.softmax_scale, ctx.causal)
+        _lib.maybe_check_status()
         return dq, dk, dv, None, None, None, None, None, None, None, None
 
 

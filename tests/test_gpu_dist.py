@@ -1,7 +1,10 @@
-"""Multi-GPU parity tests (NCCL, one process per GPU): ring, Ulysses and hybrid
-attention, forward and backward, each rank compared with its slice of the
-full-sequence CPU oracle. Skipped when fewer than two GPUs are visible; the
-schedules themselves are also covered on CPU ranks in tests/test_host.py."""
+"""Multi-GPU parity tests (NCCL, one process per GPU, every visible GPU up to 8): ring,
+Ulysses and hybrid attention, forward and backward, each rank compared with its slice of
+the full-sequence CPU oracle (the method of the reference's
+test/test_ring_attention_full_accuracy.py:108-171), plus independence of the world size,
+bitwise repeatability and one BASELINE-sized case checked on row slices. Skipped when
+fewer than two GPUs are visible; the schedules themselves are also covered on CPU ranks
+in tests/test_host.py."""
 import os
 import socket
 import sys
@@ -70,8 +73,9 @@ def _worker(rank, world, port, ret):
             res[tag] = (max(e[:1]) <= tol and max(e[1:]) <= tol * gmax and el <= 1e-3, e, el)
 
         # ---- Ulysses (non-causal and causal), B=2 exercises the unpack kernels
-        for tag, B, S, Hq, Hkv, D, causal in (("uly_b2", 2, 1024, 8, 8, 128, False),
-                                              ("uly_gqa_causal", 1, 1024, 8, 4, 128, True)):
+        hw = max(4, world)             # head counts divisible by the group size
+        for tag, B, S, Hq, Hkv, D, causal in (("uly_b2", 2, 1024, 2 * hw, 2 * hw, 128, False),
+                                              ("uly_gqa_causal", 1, 1024, 2 * hw, hw, 128, True)):
             q = _rand((B, S, Hq, D), 4).bfloat16()
             k = _rand((B, S, Hkv, D), 5).bfloat16()
             v = _rand((B, S, Hkv, D), 6).bfloat16()
@@ -89,8 +93,8 @@ def _worker(rank, world, port, ret):
             res[tag] = (max(e[:1]) <= 2e-2 and max(e[1:]) <= 2e-2 * gmax and el <= 1e-3, e, el)
 
         # ---- all-to-all bit exactness on the GPU (pack kernel + NCCL + unpack kernel)
-        x = (torch.arange(2 * 64 * 4 * 64, dtype=torch.float32).view(2, 64, 4, 64) + 1e6 * rank).to(dev)
-        ins = [(torch.arange(2 * 64 * 4 * 64, dtype=torch.float32).view(2, 64, 4, 64) + 1e6 * r)
+        x = (torch.arange(2 * 64 * hw * 64, dtype=torch.float32).view(2, 64, hw, 64) + 1e6 * rank).to(dev)
+        ins = [(torch.arange(2 * 64 * hw * 64, dtype=torch.float32).view(2, 64, hw, 64) + 1e6 * r)
                for r in range(world)]
         y = spa.all_to_all_4D(x, 2, 1)
         z = spa.all_to_all_4D(y, 1, 2)
@@ -101,7 +105,7 @@ def _worker(rank, world, port, ret):
         for tag, U, R in (("hyb_u", world, 1), ("hyb_r", 1, world)):
             spa.destroy_seq_parallel_pg()
             spa.set_seq_parallel_pg(U, R, rank, world)
-            B, S, H, D = 1, 1024, 4, 128
+            B, S, H, D = 1, 1024, hw, 128
             qkv = _rand((B, S, 3, H, D), 8).bfloat16()
             ro, rl = orc.attention_ref(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], None, True)
             sl = sl_of(S)
@@ -130,6 +134,103 @@ def _worker(rank, world, port, ret):
         gmax = max(1.0, float(rdv.abs().max()) / 4)
         res["hyb_bwd"] = (e[0] <= 2e-2 and max(e[1:]) <= 2e-2 * gmax, e, 0.0)
         spa.destroy_seq_parallel_pg()
+
+        # ---- cfg5's split (Ulysses 4 inside, ring 2 across) when 8 GPUs are visible
+        if world == 8:
+            spa.set_seq_parallel_pg(4, 2, rank, world)
+            B, S, H, D = 1, 8192, 16, 128
+            qkv = _rand((B, S, 3, H, D), 30).bfloat16()
+            ro, rl = orc.attention_ref(qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2], None, True,
+                                       dtype=torch.float32)
+            sl = sl_of(S)
+            out, lse, _ = spa.LongContextAttentionQKVPacked()(qkv[:, sl].to(dev), causal=True,
+                                                              return_attn_probs=True)
+            spa.check_status()
+            e = _errs([(out, ro[:, sl])])
+            el = _errs([(lse, rl[:, :, sl])])[0]
+            res["hyb_u4r2"] = (e[0] <= 2e-2 and el <= 1e-3, e, el)
+            spa.destroy_seq_parallel_pg()
+        else:
+            res["hyb_u4r2"] = (True, ["needs 8 GPUs"], 0.0)
+
+        # ---- independence of the world size: the ring over all ranks, rings over pairs of
+        # ranks and one GPU alone give the same numbers on the same global tensors
+        B, S, Hq, Hkv, D = 1, 2048, 8, 2, 128
+        q = _rand((B, S, Hq, D), 41).bfloat16()
+        kv = _rand((B, S, 2, Hkv, D), 42).bfloat16()
+        do = _rand((B, S, Hq, D), 43).bfloat16()
+
+        def ring_run(group, w, r):
+            sl = slice(r * (S // w), (r + 1) * (S // w))
+            ql = q[:, sl].to(dev).requires_grad_(True)
+            kvl = kv[:, sl].to(dev).requires_grad_(True)
+            out, lse, _ = spa.sp_aurora_kvpacked_func(ql, kvl, causal=True, return_attn_probs=True,
+                                                      group=group, deterministic=True)
+            out.backward(do[:, sl].to(dev))
+            return sl, [out.detach(), lse, ql.grad, kvl.grad]
+
+        sl_w, full = ring_run(None, world, rank)
+        sl_w2, again = ring_run(None, world, rank)
+        res["run_twice_bitwise"] = (all(torch.equal(a, b) for a, b in zip(full, again)), [], 0.0)
+        qf, kvf = q.to(dev).requires_grad_(True), kv.to(dev).requires_grad_(True)
+        o1, l1 = spa.flash_attn_forward(qf, kvf[:, :, 0], kvf[:, :, 1], None, True)
+        g1 = spa.flash_attn_backward(do.to(dev), qf, kvf[:, :, 0], kvf[:, :, 1], o1, l1, None, True)
+        one = [o1[:, sl_w], l1[:, :, sl_w], g1[0][:, sl_w], torch.stack((g1[1], g1[2]), dim=2)[:, sl_w]]
+        diffs = [float((a.float() - b.float()).abs().max()) for a, b in zip(full, one)]
+        pair_diffs = [0.0] * 4
+        pairs = [dist.new_group([2 * i, 2 * i + 1]) for i in range(world // 2)]   # collective
+        if world >= 4:
+            sl_p, pr = ring_run(pairs[rank // 2], 2, rank % 2)
+            ref2 = [o1[:, sl_p], l1[:, :, sl_p], g1[0][:, sl_p], torch.stack((g1[1], g1[2]), dim=2)[:, sl_p]]
+            pair_diffs = [float((a.float() - b.float()).abs().max()) for a, b in zip(pr, ref2)]
+        spa.check_status()
+        gmax = max(1.0, float(g1[2].float().abs().max()) / 4)
+        ok = all(d <= 2e-2 * (gmax if i >= 2 else 1.0) for i, d in enumerate(diffs) if i != 1) and \
+            diffs[1] <= 1e-3 and pair_diffs[1] <= 1e-3 and \
+            all(d <= 2e-2 * (gmax if i >= 2 else 1.0) for i, d in enumerate(pair_diffs) if i != 1)
+        res["world_size_independence"] = (ok, diffs + pair_diffs, 0.0)
+
+        # ---- BASELINE cfg2 at its stated size: bf16 B1 S=32768 H32 D128 causal over all ranks;
+        # 64-row slices of out / lse / dq per rank against the oracle, dk / dv of the last 64
+        # keys on the last rank, and the two checksum identities for dk / dv of every key
+        B, S, H, D = 1, 32768, 32, 128
+        sl = sl_of(S)
+        lo, n = sl.start, sl.stop - sl.start
+        gens = [torch.Generator().manual_seed(900 + i) for i in range(3)]
+        qg, kg, vg = (torch.randn(B, S, H, D, generator=g).bfloat16() for g in gens)
+        dog = torch.randn(B, S, H, D, generator=torch.Generator().manual_seed(903)).bfloat16()
+        ql, kl, vl = (t[:, sl].to(dev).requires_grad_(True) for t in (qg, kg, vg))
+        out, lse, _ = spa.sp_aurora_func(ql, kl, vl, causal=True, return_attn_probs=True)
+        out.backward(dog[:, sl].to(dev))
+        spa.check_status()
+        errs = [0.0] * 5
+        tol_g = 2e-2
+        for r0 in (n // 2, n - 64):
+            g0 = lo + r0
+            rows = slice(r0, r0 + 64)
+            ro, rl = orc.attention_ref(qg[:, g0:g0 + 64], kg[:, :g0 + 64], vg[:, :g0 + 64], None, True,
+                                       causal_off=g0, dtype=torch.float32)
+            rdq, rdk, rdv = orc.attention_bwd_ref(dog[:, g0:g0 + 64], qg[:, g0:g0 + 64], kg[:, :g0 + 64],
+                                                  vg[:, :g0 + 64], ro, rl, None, True, causal_off=g0,
+                                                  dtype=torch.float32)
+            e = _errs([(out[:, rows], ro), (lse[:, :, rows], rl), (ql.grad[:, rows], rdq)])
+            errs[:3] = [max(a, b) for a, b in zip(errs[:3], e)]
+            tol_g = max(tol_g, 2e-2 * float(rdq.abs().max()) / 4)
+            if rank == world - 1 and r0 == n - 64:
+                e = _errs([(kl.grad[:, rows], rdk[:, g0:g0 + 64]), (vl.grad[:, rows], rdv[:, g0:g0 + 64])])
+                errs[3:] = e
+                tol_g = max(tol_g, 2e-2 * float(rdv[:, g0:g0 + 64].abs().max()) / 4)
+
+        def sums(a, b):
+            p = a.float() * b.float()
+            return torch.stack((p.sum(dtype=torch.float64), p.abs().sum(dtype=torch.float64)))
+        t = torch.stack((sums(ql.grad, ql), sums(kl.grad, kl), sums(vl.grad, vl), sums(dog[:, sl].to(dev), out)))
+        dist.all_reduce(t)
+        t = t.cpu()
+        i1 = float((t[0, 0] - t[1, 0]).abs() / torch.maximum(t[0, 1], t[1, 1]))
+        i2 = float((t[2, 0] - t[3, 0]).abs() / torch.maximum(t[2, 1], t[3, 1]))
+        ok = errs[0] <= 2e-2 and errs[1] <= 1e-3 and max(errs[2:]) <= tol_g and i1 <= 1e-3 and i2 <= 1e-3
+        res["cfg2_full_size"] = (ok, errs + [i1, i2], errs[1])
     except Exception:  # noqa: BLE001
         res["error"] = traceback.format_exc()
     ret[rank] = res
@@ -142,7 +243,7 @@ def results():
     n = torch.cuda.device_count()
     if n < 2:
         pytest.skip("needs at least two GPUs")
-    world = 4 if n >= 4 else 2
+    world = 8 if n >= 8 else 4 if n >= 4 else 2
     mgr = mp.Manager()
     ret = mgr.dict()
     mp.spawn(_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
@@ -153,8 +254,10 @@ def results():
 
 
 @pytest.mark.parametrize("tag", ["ring_fp32", "ring_bf16_gqa", "ring_bf16_gqa_contig", "ring_bf16_noncausal", "uly_b2",
-                                 "uly_gqa_causal", "a2a_exact", "hyb_u", "hyb_r", "hyb_bwd"])
-def test_multi_gpu_parity(results, tag):
+                                 "uly_gqa_causal", "a2a_exact", "hyb_u", "hyb_r", "hyb_bwd", "hyb_u4r2",
+                                 "run_twice_bitwise", "world_size_independence", "cfg2_full_size"])
+def test_multi_gpu_parity(results, tag, error_log):
     for r, res in results.items():
         ok, errs, el = res[tag]
+        error_log[f"dist {tag} rank{r}"] = {"errs": errs, "lse": el}
         assert ok, f"rank {r} {tag}: errs {errs} lse {el}"

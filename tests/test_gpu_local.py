@@ -324,3 +324,23 @@ def test_long_sequence_slices_against_oracle(spa):
         if r0 == S - 128:   # only these rows see the last 128 keys: their dk/dv are complete
             assert (dk[:, rows].cpu().double() - rdk[:, rows]).abs().max() <= lim
             assert (dv[:, rows].cpu().double() - rdv[:, rows]).abs().max() <= lim
+
+
+def test_bounded_wait_gives_up_and_reports(spa):
+    """A device-side wait on a barrier that nothing arrives at runs out of its cycle budget:
+    the kernel returns normally, spa_check_status() reports SPA_ETIMEOUT with the site and
+    iteration of the wait, the status word is cleared by that read, and the next attention
+    call on the same context is correct."""
+    import ctypes as C
+    from sp_aurora_b200 import _lib
+    fn = _lib.lib.spa_internal_wait_selftest
+    fn.restype, fn.argtypes = C.c_int, [C.c_void_p, C.c_void_p]
+    spa.check_status()                                   # clean before
+    flag = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert fn(flag.data_ptr(), _lib.stream_ptr(flag.device)) == 0
+    torch.cuda.synchronize()                             # the kernel ended by itself
+    assert int(flag.item()) == 1                         # ... after its wait gave up
+    with pytest.raises(_lib.SpaError, match="site 99 iteration 7"):
+        spa.check_status()
+    spa.check_status()                                   # the read cleared the word
+    _check_fwd(spa, 1, 256, 256, 2, 2, 128, torch.bfloat16, True)
