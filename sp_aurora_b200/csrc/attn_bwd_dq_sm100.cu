@@ -73,7 +73,7 @@ struct DqSmem {
   static constexpr int kDoOff = 0;
   static constexpr int kKVOff = kDoOff + kTile;
   static constexpr int kBarOff = kKVOff + kStages * kStageBytes;
-  static constexpr int kNumBars = 2 + 2 * kStages + 7;
+  static constexpr int kNumBars = 2 + 2 * kStages + 4;
   static constexpr int kTotal = kBarOff + kNumBars * 8 + 16;
 };
 
@@ -105,11 +105,9 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
   uint64_t* q_ready = bars + 1;
   uint64_t* kv_full = bars + 2;
   uint64_t* kv_empty = kv_full + kStages;
-  uint64_t* s_full = kv_empty + kStages;
-  uint64_t* dp_full = s_full + 1;
-  uint64_t* s_free = dp_full + 1;
-  uint64_t* dp_free = s_free + 1;
-  uint64_t* ds_full = dp_free + 1;
+  uint64_t* sdp_full = kv_empty + kStages;    // S(j) and dP(j) are complete
+  uint64_t* sdp_free = sdp_full + 1;          // S(j) and dP(j) are in registers
+  uint64_t* ds_full = sdp_free + 1;
   uint64_t* dq_done = ds_full + 1;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
   volatile int* cta_abort = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -145,10 +143,8 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
-    mbar_init(s_full, 1);
-    mbar_init(dp_full, 1);
-    mbar_init(s_free, kComputeThreads);
-    mbar_init(dp_free, kComputeThreads);
+    mbar_init(sdp_full, 1);
+    mbar_init(sdp_free, kComputeThreads);
     mbar_init(ds_full, kComputeThreads);
     mbar_init(dq_done, 1);
     fence_mbar_init();
@@ -211,7 +207,6 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
           const uint32_t off = ((kk / 4) * L::kSlab + (kk % 4) * 32) >> 4;
           mma_ts_d(tmem_base + kColS, tmem_base + kColQ + kk * 8, kv_km, b0 + off, idesc_s, kk > 0);
         }
-        mma_commit(s_full);
         return true;
       };
       // dP(j) = dO V_j^T : A = dO tile (shared memory), B = V tile (K-major).
@@ -222,7 +217,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
           const uint32_t off = ((kk / 4) * L::kSlab + (kk % 4) * 32) >> 4;
           mma_ss_d(tmem_base + kColDP, do_km, off, kv_km, b0 + off, idesc_s, kk > 0);
         }
-        mma_commit(dp_full);
+        mma_commit(sdp_full);
       };
 
       if (ok) ok = issue_s(0, 0);
@@ -233,14 +228,11 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
           const int j = j0 + sl;
           if (j >= n_kv || !ok) break;
           if (j + 1 < n_kv) {
-            ok = mbar_wait(s_free, j & 1, wc, 4, j);      // S(j) is in registers
+            ok = mbar_wait(sdp_free, j & 1, wc, 4, j);    // S(j) and dP(j) are in registers
             if (!ok) break;
             tc_fence_after();
             ok = issue_s(j + 1, (sl + 1) % kStages);
             if (!ok) break;
-            ok = mbar_wait(dp_free, j & 1, wc, 5, j);     // dP(j) is in registers
-            if (!ok) break;
-            tc_fence_after();
             issue_dp((sl + 1) % kStages);
           }
           ok = mbar_wait(ds_full, j & 1, wc, 6, j);
@@ -302,24 +294,18 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
     const float dlt = row_ok ? p.delta[sidx] : 0.f;
 
     for (int j = 0; j < n_kv; ++j) {
-      ok = warp_wait(s_full, j & 1, wc, 8, j);
+      // dP(j) follows S(j) on the in-order tensor pipe, so its completion covers both. Both are
+      // taken into registers before the exponentials: the issuer can then put S(j+1) and
+      // dP(j+1) on the pipe back to back while this tile is turned into dS.
+      ok = warp_wait(sdp_full, j & 1, wc, 8, j);
       if (!ok) break;
       tc_fence_after();
-      uint32_t sr[32];
+      uint32_t sr[32], dpr[32];
       tmem_ld32(t_s, sr);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(s_free);
-      // dP(j) is taken into registers before the exponentials, not after: the issuer can then
-      // put S(j+1) and dP(j+1) on the tensor pipe back to back while this tile is turned into dS.
-      ok = warp_wait(dp_full, j & 1, wc, 9, j);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t dpr[32];
       tmem_ld32(t_dp, dpr);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(dp_free);
+      mbar_arrive(sdp_free);
       float* pr = reinterpret_cast<float*>(sr);   // scores, then probabilities, in place
 
       const int k0 = j * kTileN;

@@ -67,10 +67,12 @@ struct WaitCtx {
 // which case the caller must skip its work and fall through to the exit path.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w,
                                           int site, int iter) {
-  if (*w.cta_abort) return false;
-  // Fast path without reading the clock (a clock read before every wait costs ~15 % of
-  // kernel time).
+  // Fast path: one try_wait, no shared-memory read and no clock read (a clock read before
+  // every wait costs ~15 % of kernel time, and every extra shared-memory round trip adds
+  // to a latency that each pipeline hop pays). A CTA that has aborted reaches the slow
+  // path at its next unsatisfied wait and leaves there.
   if (mbar_try_wait(bar, parity)) return true;
+  if (*w.cta_abort) return false;
   const long long t0 = clock64();
   uint32_t spins = 0;
   while (true) {
@@ -144,10 +146,6 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, const void* s
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
-// Wait until the source shared memory of all committed bulk groups was read.
-__device__ __forceinline__ void bulk_wait_read_all() {
-  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-}
 // Wait until all committed bulk groups have completed (writes performed).
 __device__ __forceinline__ void bulk_wait_all() {
   asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -190,17 +188,6 @@ __device__ __forceinline__ void tc_fence_after() {
 //   between 8-row K groups (1024); LBO = bytes between successive 64-element
 //   column slabs; advance K by 16 rows = +2048 B.
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes,
-                                                    uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
-  d |= 1ull << 46;
-  d |= 2ull << 61;
-  return d;
-}
-
 // The same descriptor split into its two 32-bit words, so that the issuing thread
 // can step through a tile by adding a (compile-time) constant to the low word
 // instead of rebuilding 64 bits per MMA: byte offset `off` -> lo + (off >> 4).
@@ -225,16 +212,8 @@ __host__ __device__ constexpr uint32_t make_idesc(int m, int n, bool bf16, bool 
          (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread.
-__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Same, operands given as split descriptors plus offsets in 16-byte units.
+// D[tmem] (+)= A[smem] * B[smem]; issued by ONE thread. Operands are split descriptors
+// plus offsets in 16-byte units.
 __device__ __forceinline__ void mma_ss_d(uint32_t d_tmem, SmemDesc a, uint32_t a_off16, SmemDesc b,
                                          uint32_t b_off16, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -245,6 +224,8 @@ __device__ __forceinline__ void mma_ss_d(uint32_t d_tmem, SmemDesc a, uint32_t a
       "r"(a.lo + a_off16), "r"(a.hi), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// D[tmem] (+)= A[tmem] * B[smem]; A is read from tensor memory (rows = TMEM lanes, 16-bit
+// elements packed two per 32-bit column, 8 columns per K=16 step).
 __device__ __forceinline__ void mma_ts_d(uint32_t d_tmem, uint32_t a_tmem, SmemDesc b,
                                          uint32_t b_off16, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -253,50 +234,6 @@ __device__ __forceinline__ void mma_ts_d(uint32_t d_tmem, uint32_t a_tmem, SmemD
       "setp.ne.b32 p, %5, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
       "r"(a_tmem), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Warp-uniform variants: every lane of the issuing warp executes the statement
-// with identical operands (so the compiler can keep descriptors in uniform
-// registers) and the instruction itself is predicated on `leader`.
-__device__ __forceinline__ void mma_ss_u(uint32_t d_tmem, SmemDesc a, uint32_t a_off16, SmemDesc b,
-                                         uint32_t b_off16, uint32_t idesc, uint32_t accumulate,
-                                         uint32_t leader) {
-  asm volatile(
-      "{\n\t.reg .pred p, lp;\n\t.reg .b64 da, db;\n\t"
-      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-      "setp.ne.b32 p, %6, 0;\n\tsetp.ne.b32 lp, %7, 0;\n\t"
-      "@lp tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
-      "r"(a.lo + a_off16), "r"(a.hi), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc), "r"(accumulate),
-      "r"(leader)
-      : "memory");
-}
-__device__ __forceinline__ void mma_ts_u(uint32_t d_tmem, uint32_t a_tmem, SmemDesc b,
-                                         uint32_t b_off16, uint32_t idesc, uint32_t accumulate,
-                                         uint32_t leader) {
-  asm volatile(
-      "{\n\t.reg .pred p, lp;\n\t.reg .b64 db;\n\t"
-      "mov.b64 db, {%2, %3};\n\t"
-      "setp.ne.b32 p, %5, 0;\n\tsetp.ne.b32 lp, %6, 0;\n\t"
-      "@lp tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "r"(b.lo + b_off16), "r"(b.hi), "r"(idesc), "r"(accumulate), "r"(leader)
-      : "memory");
-}
-__device__ __forceinline__ void mma_commit_u(uint64_t* bar, uint32_t leader) {
-  asm volatile(
-      "{\n\t.reg .pred lp;\n\tsetp.ne.b32 lp, %1, 0;\n\t"
-      "@lp tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(
-          smem_u32(bar)),
-      "r"(leader)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]; A is read from tensor memory (rows = TMEM
-// lanes, 16-bit elements packed two per 32-bit column, 8 columns per K=16 step).
-__device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                       uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
-      "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
 // Arrive on `bar` when every tcgen05 operation issued so far by this thread
@@ -394,12 +331,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-
-// Byte offset of the 16-byte chunk holding elements [8*chunk, 8*chunk+8) of
-// row `row` inside a 128-byte-swizzled slab (rows of 64 two-byte elements).
-__device__ __forceinline__ uint32_t sw128_chunk_off(uint32_t row, uint32_t chunk) {
-  return row * 128u + ((chunk ^ (row & 7u)) << 4);
 }
 
 }  // namespace spa
