@@ -192,6 +192,7 @@ def run_aux(args):
     peak = peaks.get("hbm_gbs", FALLBACK_PEAKS["hbm_gbs"])
     Bq, S, H, Dh, P = args.aux_batch, 8192, 32, 128, 8   # batch 2 = cfg3: one rank's [2,8192,32,128] bf16 shard
     x = torch.randn(Bq, S, H, Dh, device="cuda").bfloat16()
+    y = torch.randn(Bq, S, H, Dh, device="cuda").bfloat16()
     send = torch.empty((P, Bq, S, H // P, Dh), dtype=x.dtype, device="cuda")
     src = x.unflatten(2, (P, H // P)).permute(2, 0, 1, 3, 4)
     outp = torch.empty((Bq, S, H, Dh), dtype=x.dtype, device="cuda")
@@ -220,7 +221,7 @@ def run_aux(args):
                                                                           send.permute(1, 2, 0, 3, 4)), 2 * nbytes),
             ("merge (fp32 acc r/w + bf16 block + 3 lse)", lambda: la.update_out_and_lse(acc, lse, x, blse),
              x.numel() * (4 + 4 + 2) + rows * 12),
-            ("delta (rowsum dO*O)", lambda: la.bwd_delta(x, x), 2 * nbytes + rows * 4),
+            ("delta (rowsum dO*O)", lambda: la.bwd_delta(x, y), 2 * nbytes + rows * 4),
             ("cast fp32->bf16", lambda: la.cast_from_f32(acc, torch.bfloat16, 1.0, outp), x.numel() * 6)):
         t = timeit(fn)
         res[name] = {"ms": t * 1e3, "algorithmic_bytes": traffic, "algorithmic_GBps": traffic / t / 1e9,

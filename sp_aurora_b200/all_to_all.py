@@ -23,7 +23,7 @@ from ._lib import check, lib
 
 __all__ = ["all_to_all_4D", "all_to_all_5D", "SeqAllToAll4D", "SeqAllToAll5D",
            "seq_all_to_all_4d_inference", "strided_copy", "heads_all_to_all_packed",
-           "seq_all_to_all_packed"]
+           "seq_all_to_all_packed", "HeadsAllToAllPacked"]
 
 
 def _coalesce(shape, sst, dst):
@@ -240,6 +240,23 @@ def seq_all_to_all_packed(tensors, group=None, copy_fn: Callable = strided_copy)
         outs.append(out)
         o += h
     return outs
+
+
+class HeadsAllToAllPacked(torch.autograd.Function):
+    """Autograd form of heads_all_to_all_packed: `apply(group, q, k, v)` reshards the
+    tensors sequence -> heads as one message and returns views of the gathered buffer; the
+    gradients go back head -> sequence as one message too."""
+
+    @staticmethod
+    def forward(ctx, group, *tensors):
+        ctx.group = group
+        outs = heads_all_to_all_packed(tensors, group=group)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        grads = [g if g.stride(-1) == 1 else g.contiguous() for g in grads]
+        return (None, *seq_all_to_all_packed(grads, group=ctx.group))
 
 
 class SeqAllToAll4D(torch.autograd.Function):

@@ -272,34 +272,56 @@ __device__ __forceinline__ RowIdx decode_row(Idx row, int S, int H) {
   return r;
 }
 
-// 8 elements (16 bytes for 2-byte types) per thread; D/8 consecutive threads share a row.
+// The pack/unpack copy keeps kVecPerThread independent 16-byte accesses in flight per
+// thread (a block sweeps kVecPerThread coalesced runs of blockDim vectors) with the
+// streaming (evict-first) hint.
+constexpr int kVecPerThread = 4;
+constexpr int kStreamBlock = 256;
+
+inline long long stream_grid(long long n_vec) {
+  const long long per_block = (long long)kStreamBlock * kVecPerThread;
+  return (n_vec + per_block - 1) / per_block;
+}
+
+// 16 bytes of 2-byte elements (or 32 bytes of fp32) of two rows -> their partial dot product.
 template <typename T>
-__device__ __forceinline__ float dot8(const T* a, const T* b);
+struct Vec8 {
+  uint4 lo, hi;   // hi is used by fp32 only
+};
+template <typename T>
+__device__ __forceinline__ Vec8<T> load8(const T* p) {
+  Vec8<T> v;
+  v.lo = __ldcs(reinterpret_cast<const uint4*>(p));
+  if (sizeof(T) == 4) v.hi = __ldcs(reinterpret_cast<const uint4*>(p) + 1); else v.hi = v.lo;
+  return v;
+}
+template <typename T>
+__device__ __forceinline__ float dot8(const Vec8<T>& a, const Vec8<T>& b);
 template <>
-__device__ __forceinline__ float dot8<float>(const float* a, const float* b) {
-  const float4 a0 = *reinterpret_cast<const float4*>(a), a1 = *reinterpret_cast<const float4*>(a + 4);
-  const float4 b0 = *reinterpret_cast<const float4*>(b), b1 = *reinterpret_cast<const float4*>(b + 4);
-  return a0.x * b0.x + a0.y * b0.y + a0.z * b0.z + a0.w * b0.w + a1.x * b1.x + a1.y * b1.y +
-         a1.z * b1.z + a1.w * b1.w;
+__device__ __forceinline__ float dot8<float>(const Vec8<float>& a, const Vec8<float>& b) {
+  const float* x = reinterpret_cast<const float*>(&a.lo);
+  const float* y = reinterpret_cast<const float*>(&b.lo);
+  const float* z = reinterpret_cast<const float*>(&a.hi);
+  const float* w = reinterpret_cast<const float*>(&b.hi);
+  return x[0] * y[0] + x[1] * y[1] + x[2] * y[2] + x[3] * y[3] + z[0] * w[0] + z[1] * w[1] +
+         z[2] * w[2] + z[3] * w[3];
 }
 template <>
-__device__ __forceinline__ float dot8<__nv_bfloat16>(const __nv_bfloat16* a, const __nv_bfloat16* b) {
-  const uint4 ua = *reinterpret_cast<const uint4*>(a), ub = *reinterpret_cast<const uint4*>(b);
-  const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+__device__ __forceinline__ float dot8<__nv_bfloat16>(const Vec8<__nv_bfloat16>& a,
+                                                     const Vec8<__nv_bfloat16>& b) {
+  const uint32_t wa[4] = {a.lo.x, a.lo.y, a.lo.z, a.lo.w}, wb[4] = {b.lo.x, b.lo.y, b.lo.z, b.lo.w};
   float acc = 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wa[i]));
-    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wb[i]));
-    acc = fmaf(x.x, y.x, acc);
-    acc = fmaf(x.y, y.y, acc);
+    // a bf16 is the upper half of an fp32: two shifts / masks per pair instead of conversions
+    acc = fmaf(__uint_as_float(wa[i] << 16), __uint_as_float(wb[i] << 16), acc);
+    acc = fmaf(__uint_as_float(wa[i] & 0xffff0000u), __uint_as_float(wb[i] & 0xffff0000u), acc);
   }
   return acc;
 }
 template <>
-__device__ __forceinline__ float dot8<__half>(const __half* a, const __half* b) {
-  const uint4 ua = *reinterpret_cast<const uint4*>(a), ub = *reinterpret_cast<const uint4*>(b);
-  const uint32_t wa[4] = {ua.x, ua.y, ua.z, ua.w}, wb[4] = {ub.x, ub.y, ub.z, ub.w};
+__device__ __forceinline__ float dot8<__half>(const Vec8<__half>& a, const Vec8<__half>& b) {
+  const uint32_t wa[4] = {a.lo.x, a.lo.y, a.lo.z, a.lo.w}, wb[4] = {b.lo.x, b.lo.y, b.lo.z, b.lo.w};
   float acc = 0.f;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -311,57 +333,67 @@ __device__ __forceinline__ float dot8<__half>(const __half* a, const __half* b) 
   return acc;
 }
 
-// The pack/unpack copy keeps kVecPerThread independent 16-byte accesses in flight per
-// thread (a block sweeps kVecPerThread coalesced runs of blockDim vectors) with the
-// streaming (evict-first) hint. The same unrolling made delta, merge and cast slower
-// (measured), so those stay one vector per thread.
-constexpr int kVecPerThread = 4;
-constexpr int kStreamBlock = 256;
-
-inline long long stream_grid(long long n_vec) {
-  const long long per_block = (long long)kStreamBlock * kVecPerThread;
-  return (n_vec + per_block - 1) / per_block;
-}
+// delta: one thread per 8 elements, D/8 consecutive threads share a row; kRowsInFlight rows
+// per thread with every load issued before the first use (the row of a thread in pass u is
+// its first row + u * rows-per-pass, so every pass is coalesced).
+constexpr int kRowsInFlight = 4;
 
 template <typename T, typename Idx>
-__global__ void delta_kernel(const T* __restrict__ out, int64_t o_sb, int64_t o_ss, int64_t o_sh,
-                             const T* __restrict__ dout, int64_t d_sb, int64_t d_ss, int64_t d_sh,
-                             float* __restrict__ delta, int B, int S, int H, int D) {
+__global__ void __launch_bounds__(256)
+delta_kernel(const T* __restrict__ out, int64_t o_sb, int64_t o_ss, int64_t o_sh,
+             const T* __restrict__ dout, int64_t d_sb, int64_t d_ss, int64_t d_sh,
+             float* __restrict__ delta, int B, int S, int H, int D) {
   const int tpr = D / 8;
-  const Idx gid = (Idx)blockIdx.x * blockDim.x + threadIdx.x;
-  const Idx row = gid / (Idx)tpr;
-  const int c = (int)(gid % (Idx)tpr) * 8;
   const Idx nrows = (Idx)B * S * H;
-  float acc = 0.f;
-  RowIdx r = {0, 0, 0};
-  if (row < nrows) {
-    r = decode_row<Idx>(row, S, H);
-    acc = dot8<T>(out + r.b * o_sb + r.s * o_ss + r.h * o_sh + c,
-                  dout + r.b * d_sb + r.s * d_ss + r.h * d_sh + c);
+  const Idx rows_per_pass = ((Idx)gridDim.x * blockDim.x) / (Idx)tpr;
+  const Idx gid = (Idx)blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = (int)(gid % (Idx)tpr) * 8;
+  Vec8<T> a[kRowsInFlight], b[kRowsInFlight];
+  size_t di[kRowsInFlight];
+  bool ok[kRowsInFlight];
+#pragma unroll
+  for (int u = 0; u < kRowsInFlight; ++u) {
+    const Idx row = gid / (Idx)tpr + (Idx)u * rows_per_pass;
+    ok[u] = row < nrows;
+    const RowIdx r = decode_row<Idx>(ok[u] ? row : 0, S, H);
+    di[u] = ((size_t)r.b * H + r.h) * S + r.s;
+    if (ok[u]) {
+      a[u] = load8<T>(out + r.b * o_sb + r.s * o_ss + r.h * o_sh + c);
+      b[u] = load8<T>(dout + r.b * d_sb + r.s * d_ss + r.h * d_sh + c);
+    }
   }
-  for (int o = tpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-  if (row < nrows && c == 0) delta[((size_t)r.b * H + r.h) * S + r.s] = acc;
+#pragma unroll
+  for (int u = 0; u < kRowsInFlight; ++u) {
+    float acc = ok[u] ? dot8<T>(a[u], b[u]) : 0.f;
+    for (int o = tpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (ok[u] && c == 0) delta[di[u]] = acc;
+  }
 }
 
+// merge: a warp takes 32 consecutive rows. Lane i first turns the two lse values of row i
+// into (lse', w_old, w_blk) -- the exponentials, the logarithm and the divisions are done
+// once per row, not once per element vector -- then the warp sweeps the rows, 128 floats
+// (32 lanes x float4) per pass, with the weights of each row broadcast by shuffles.
 template <typename T, typename Idx>
-__global__ void merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse,
-                             const T* __restrict__ bo, int64_t bo_sb, int64_t bo_ss, int64_t bo_sh,
-                             const float* __restrict__ blse, int B, int S, int H, int D) {
-  const int tpr = D / 4;
-  const Idx gid = (Idx)blockIdx.x * blockDim.x + threadIdx.x;
-  const Idx row = gid / (Idx)tpr;
-  const int c = (int)(gid % (Idx)tpr) * 4;
+__global__ void __launch_bounds__(256)
+merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse, const T* __restrict__ bo,
+             int64_t bo_sb, int64_t bo_ss, int64_t bo_sh, const float* __restrict__ blse, int B,
+             int S, int H, int D) {
+  const int lane = threadIdx.x & 31;
+  const Idx warp = ((Idx)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const Idx nrows = (Idx)B * S * H;
-  const bool ok = row < nrows;
-  float lse_new = 0.f;
-  size_t li = 0;
-  if (ok) {
-    const RowIdx r = decode_row<Idx>(row, S, H);
-    li = ((size_t)r.b * H + r.h) * S + r.s;
+  const Idx row0 = warp * 32;
+  if (row0 >= nrows) return;
+  // phase 1: lane i owns row row0 + i
+  const Idx my_row = row0 + lane;
+  const bool mine = my_row < nrows;
+  const RowIdx mr = decode_row<Idx>(mine ? my_row : 0, S, H);
+  const size_t li = ((size_t)mr.b * H + mr.h) * S + mr.s;
+  float w_old = 0.f, w_blk = 0.f;
+  if (mine) {
     const float lo = lse[li], lb = blse[li];
     const float mx = fmaxf(lo, lb);
-    float w_old = 0.f, w_blk = 0.f;
-    lse_new = mx;
+    float lse_new = mx;
     if (mx != -INFINITY) {
       const float eo = expf(lo - mx), eb = expf(lb - mx);
       const float sum = eo + eb;
@@ -369,15 +401,38 @@ __global__ void merge_kernel(float* __restrict__ out_acc, float* __restrict__ ls
       w_old = eo / sum;
       w_blk = eb / sum;
     }
-    float* ap = out_acc + (size_t)row * D + c;
-    const float4 a = *reinterpret_cast<const float4*>(ap);
-    const float4 x = ld4<T>(bo + r.b * bo_sb + r.s * bo_ss + r.h * bo_sh + c);
-    *reinterpret_cast<float4*>(ap) =
-        make_float4(w_old * a.x + w_blk * x.x, w_old * a.y + w_blk * x.y, w_old * a.z + w_blk * x.z,
-                    w_old * a.w + w_blk * x.w);
+    lse[li] = lse_new;
   }
-  __syncwarp();  // every thread of the row has read the old lse
-  if (ok && c == 0) lse[li] = lse_new;
+  const int64_t my_bo = mr.b * bo_sb + mr.s * bo_ss + mr.h * bo_sh;   // element offset of my row in bo
+  // phase 2: `rpp` rows per pass (a row is D/4 lanes wide), two passes in flight
+  const int lpr = D / 4, rpp = 32 / lpr;
+  const int sub = lane / lpr, c = (lane % lpr) * 4;
+  const int n = (int)min((Idx)32, nrows - row0);
+  for (int i = 0; i < n; i += 2 * rpp) {
+    float4 av[2], xv[2];
+    float wo[2], wb[2];
+    int rr[2];
+    bool ok[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      rr[u] = i + u * rpp + sub;
+      const int src = min(rr[u], 31);
+      wo[u] = __shfl_sync(0xffffffffu, w_old, src);
+      wb[u] = __shfl_sync(0xffffffffu, w_blk, src);
+      const long long off_lo = __shfl_sync(0xffffffffu, (long long)my_bo, src);
+      ok[u] = rr[u] < n;
+      if (ok[u]) {
+        av[u] = __ldcs(reinterpret_cast<const float4*>(out_acc + (size_t)(row0 + rr[u]) * D + c));
+        xv[u] = ld4<T>(bo + off_lo + c);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+      if (ok[u])
+        __stcs(reinterpret_cast<float4*>(out_acc + (size_t)(row0 + rr[u]) * D + c),
+               make_float4(wo[u] * av[u].x + wb[u] * xv[u].x, wo[u] * av[u].y + wb[u] * xv[u].y,
+                           wo[u] * av[u].z + wb[u] * xv[u].z, wo[u] * av[u].w + wb[u] * xv[u].w));
+  }
 }
 
 // Two independent 16-byte streaming loads per thread (82 -> 87 % of the copy peak).
@@ -691,10 +746,10 @@ int spa_bwd_delta(const void* out, int64_t o_sb, int64_t o_ss, int64_t o_sh, con
       return SPA_EINVAL;
     }
   }
-  const long long threads = (long long)B * S * H * (D / 8);
-  const int block = 256;
+  const long long threads = ((long long)B * S * H + kRowsInFlight - 1) / kRowsInFlight * (D / 8);
+  const int block = 256;   // a multiple of D/8: rows never straddle blocks or passes
   const long long grid = (threads + block - 1) / block;
-  const bool small = grid * block < (1ll << 31);
+  const bool small = grid * block * kRowsInFlight < (1ll << 31);
   SPA_DISPATCH_T(dtype, if (small) delta_kernel<T, uint32_t><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
                             (const T*)out, o_sb, o_ss, o_sh, (const T*)dout, do_sb, do_ss, do_sh,
                             delta, B, S, H, D);
@@ -718,7 +773,7 @@ int spa_merge(float* out_acc, float* lse, const void* block_out, int64_t bo_sb, 
     set_error("spa_merge: out_acc must be 16-byte aligned, block_out base and strides multiples of 4 elements");
     return SPA_EINVAL;
   }
-  const long long threads = (long long)B * S * H * (D / 4);
+  const long long threads = (long long)B * S * H;          // a warp per 32 rows: one thread per row
   const int block = 256;
   const long long grid = (threads + block - 1) / block;
   const bool small = grid * block < (1ll << 31);

@@ -18,7 +18,7 @@ from typing import Optional, Tuple, Union
 import torch
 import torch.distributed as dist
 
-from .all_to_all import SeqAllToAll4D, SeqAllToAll5D, reshard_lse
+from .all_to_all import HeadsAllToAllPacked, SeqAllToAll4D, SeqAllToAll5D, reshard_lse
 from .local_attn import check_unsupported_kwargs
 from .ring import ring_flash_attn_func, ring_flash_attn_qkvpacked_func
 from .ulysses import AttnType
@@ -161,15 +161,12 @@ class LongContextAttention(torch.nn.Module):
             value = joint_tensor_key_value[:, :, 1]
         upg = self.ulysses_pg if self.use_ulysses else None
         if upg is not None:
-            same = query.shape == key.shape
-            if self.use_pack_qkv and same:
-                qkv = torch.stack((query, key, value), dim=2)
-                qkv = SeqAllToAll5D.apply(upg, qkv, 3, 1, self.use_sync)
-                query, key, value = qkv[:, :, 0], qkv[:, :, 1], qkv[:, :, 2]
-            else:
-                query = SeqAllToAll4D.apply(upg, query, self.scatter_idx, self.gather_idx, self.use_sync)
-                key = SeqAllToAll4D.apply(upg, key, self.scatter_idx, self.gather_idx, self.use_sync)
-                value = SeqAllToAll4D.apply(upg, value, self.scatter_idx, self.gather_idx, self.use_sync)
+            # q, k and v (equal or GQA head counts) travel as ONE all-to-all message and are
+            # read where they land; `use_pack_qkv` therefore changes nothing here
+            # (sp_aurora/hybrid/long_ctx_attention.py:136-153 stacks or sends three).
+            if self.scatter_idx != 2 or self.gather_idx != 1:
+                raise ValueError("LongContextAttention reshards heads (2) against sequence (1)")
+            query, key, value = HeadsAllToAllPacked.apply(upg, query, key, value)
         res = ring_flash_attn_func(query, key, value, dropout_p=dropout_p,
                                    softmax_scale=softmax_scale, causal=causal,
                                    window_size=window_size, alibi_slopes=alibi_slopes,

@@ -186,6 +186,15 @@ def _worker(rank, world, port, golden, ret):
         y1 = a2a.all_to_all_4D(x1, 2, 1, copy_fn=_host_copy)
         z1 = a2a.all_to_all_4D(y1, 1, 2, copy_fn=_host_copy)
         res["a4_b1"] = torch.equal(z1, x1)
+        # q, k, v (GQA head counts) as one packed message, both directions, batch 2 and 1
+        for Bp in (2, 1):
+            ins = [[torch.arange(Bp * 8 * H * 4, dtype=torch.float32).view(Bp, 8, H, 4) + 1000 * r + 7 * t
+                    for t, H in enumerate((4, 2, 2))] for r in range(world)]
+            got = a2a.heads_all_to_all_packed(ins[rank], None, copy_fn=_host_copy)
+            want = [orc.all_to_all_4d_ref([ins[r][t] for r in range(world)], 2, 1)[rank] for t in range(3)]
+            back = a2a.seq_all_to_all_packed(got, None, copy_fn=_host_copy)
+            res[f"packed_b{Bp}"] = all(torch.equal(g, w) for g, w in zip(got, want)) and \
+                all(torch.equal(b, x) for b, x in zip(back, ins[rank]))
         lse = torch.arange(2 * 3 * 8, dtype=torch.float32).view(2, 3, 8) + 100 * rank
         rl = a2a.reshard_lse(lse, None)
         res["lse_shape"] = tuple(rl.shape) == (2, 6, 4)
@@ -248,6 +257,7 @@ def gloo_results(golden_dir):
 def test_gloo_all_to_all_bit_exact_vs_reference(gloo_results):
     for r in range(2):
         assert gloo_results[r]["a4"] and gloo_results[r]["a5"] and gloo_results[r]["a4_b1"]
+        assert gloo_results[r]["packed_b2"] and gloo_results[r]["packed_b1"]
         assert gloo_results[r]["lse_shape"]
 
 
