@@ -312,9 +312,9 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     const bool key_ok = kidx < p.Sk;
     bool ok = true;
 
-    // Row statistics of a query tile, fetched by the first 256 compute threads: threads
-    // 0-127 lse (pre-multiplied by log2 e), threads 128-255 delta. +inf lse makes
-    // out-of-range query rows give P = 0. Iteration `it` reads buffer it % 3 and fills
+    // Row statistics of a query tile, fetched by the first 256 compute threads and stored
+    // NEGATED (the packed multiply-adds below add them): threads 0-127 -lse*log2(e), threads
+    // 128-255 -delta. -inf in place of -lse makes out-of-range query rows give P = 0. Iteration `it` reads buffer it % 3 and fills
     // buffer (it + 1) % 3: a thread can be at most one iteration ahead of the slowest one
     // (it cannot pass the scores of iteration it before every thread has handed in P^T of
     // iteration it - 1), so the buffer being filled is never one that is still being read.
@@ -323,8 +323,8 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       const int hq = g * G + it / n_q;
       const int qi = (i_start + it % n_q) * kTileQ + (stat_tid & 127);
       const size_t idx = (size_t)b * p.lse_sb + (size_t)hq * p.lse_sh + qi;
-      if (stat_tid < 128) return qi < p.Sq ? p.lse[idx] * kLog2e : INFINITY;
-      return qi < p.Sq ? p.delta[idx] : 0.f;
+      if (stat_tid < 128) return qi < p.Sq ? -p.lse[idx] * kLog2e : -INFINITY;
+      return qi < p.Sq ? -p.delta[idx] : 0.f;
     };
     if (n_it > 0 && stat_tid < 256) {
       row_buf[(0 * 2 + (stat_tid >> 7)) * kTileQ + (stat_tid & 127)] = fetch_rowstat(0);
@@ -362,10 +362,13 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           float* e = pr + hh * 16 + 4 * i;    // rows g8 (e[0], e[1]) and g8 + 8 (e[2], e[3])
-          e[0] = fast_exp2(fmaf(e[0], p.scale_log2, -lv[i].x));
-          e[1] = fast_exp2(fmaf(e[1], p.scale_log2, -lv[i].y));
-          e[2] = fast_exp2(fmaf(e[2], p.scale_log2, -lv[i].x));
-          e[3] = fast_exp2(fmaf(e[3], p.scale_log2, -lv[i].y));
+          float x0, x1, x2, x3;
+          fma2(x0, x1, e[0], e[1], p.scale_log2, p.scale_log2, lv[i].x, lv[i].y);
+          fma2(x2, x3, e[2], e[3], p.scale_log2, p.scale_log2, lv[i].x, lv[i].y);
+          e[0] = fast_exp2(x0);
+          e[1] = fast_exp2(x1);
+          e[2] = fast_exp2(x2);
+          e[3] = fast_exp2(x3);
         }
       if (need_mask) {
 #pragma unroll
@@ -416,10 +419,11 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const float* e = pr + hh * 16 + 4 * i;
-          const float d0 = e[0] * (__uint_as_float(dpr[4 * i]) - dl[i].x);
-          const float d1 = e[1] * (__uint_as_float(dpr[4 * i + 1]) - dl[i].y);
-          const float d2 = e[2] * (__uint_as_float(dpr[4 * i + 2]) - dl[i].x);
-          const float d3 = e[3] * (__uint_as_float(dpr[4 * i + 3]) - dl[i].y);
+          float t0, t1, t2, t3, d0, d1, d2, d3;
+          add2(t0, t1, __uint_as_float(dpr[4 * i]), __uint_as_float(dpr[4 * i + 1]), dl[i].x, dl[i].y);
+          add2(t2, t3, __uint_as_float(dpr[4 * i + 2]), __uint_as_float(dpr[4 * i + 3]), dl[i].x, dl[i].y);
+          mul2(d0, d1, e[0], e[1], t0, t1);
+          mul2(d2, d3, e[2], e[3], t2, t3);
           dsp[hh * 8 + 2 * i] = pack2<T>(d0, d1);
           dsp[hh * 8 + 2 * i + 1] = pack2<T>(d2, d3);
         }

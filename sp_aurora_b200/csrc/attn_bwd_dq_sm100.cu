@@ -288,10 +288,11 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
       tc_fence_before();
       mbar_arrive(q_ready);
     }
-    // Row statistics: +inf lse makes out-of-range rows give P = 0.
+    // Row statistics, negated for the packed multiply-adds: -inf in place of -lse makes
+    // out-of-range rows give P = 0.
     const size_t sidx = (size_t)b * p.lse_sb + (size_t)h * p.lse_sh + (row_ok ? qrow : 0);
-    const float lse2 = row_ok ? p.lse[sidx] * kLog2e : INFINITY;
-    const float dlt = row_ok ? p.delta[sidx] : 0.f;
+    const float nlse2 = row_ok ? -p.lse[sidx] * kLog2e : -INFINITY;
+    const float ndlt = row_ok ? -p.delta[sidx] : 0.f;
 
     for (int j = 0; j < n_kv; ++j) {
       // dP(j) follows S(j) on the in-order tensor pipe, so its completion covers both. Both are
@@ -314,22 +315,30 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
           (p.causal && ((long long)k0 + kTileN - 1 > (long long)q0 + p.causal_off));
       if (!need_mask) {                            // tiles below the diagonal: no selects
 #pragma unroll
-        for (int c = 0; c < 32; ++c) pr[c] = fast_exp2(fmaf(pr[c], p.scale_log2, -lse2));
+        for (int c = 0; c < 32; c += 2) {
+          float x0, x1;
+          fma2(x0, x1, pr[c], pr[c + 1], p.scale_log2, p.scale_log2, nlse2, nlse2);
+          pr[c] = fast_exp2(x0);
+          pr[c + 1] = fast_exp2(x1);
+        }
       } else {
         long long lim = p.Sk - 1;
         if (p.causal) lim = min(lim, (long long)qrow + p.causal_off);
         const int limit = (int)max(0ll, min(lim - k0 - c_base + 1, 32ll));   // first masked column
 #pragma unroll
-        for (int c = 0; c < 32; ++c) {
-          const float pe = fast_exp2(fmaf(pr[c], p.scale_log2, -lse2));
-          pr[c] = c < limit ? pe : 0.f;
+        for (int c = 0; c < 32; c += 2) {
+          float x0, x1;
+          fma2(x0, x1, pr[c], pr[c + 1], p.scale_log2, p.scale_log2, nlse2, nlse2);
+          pr[c] = c < limit ? fast_exp2(x0) : 0.f;
+          pr[c + 1] = c + 1 < limit ? fast_exp2(x1) : 0.f;
         }
       }
       uint32_t dsp[16];
 #pragma unroll
       for (int c = 0; c < 32; c += 2) {
-        const float d0 = pr[c] * (__uint_as_float(dpr[c]) - dlt);
-        const float d1 = pr[c + 1] * (__uint_as_float(dpr[c + 1]) - dlt);
+        float e0, e1, d0, d1;
+        add2(e0, e1, __uint_as_float(dpr[c]), __uint_as_float(dpr[c + 1]), ndlt, ndlt);
+        mul2(d0, d1, pr[c], pr[c + 1], e0, e1);
         dsp[c >> 1] = pack2<T>(d0, d1);
       }
       if (j > 0) {

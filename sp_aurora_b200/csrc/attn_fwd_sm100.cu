@@ -313,37 +313,38 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       }
       const float m_eff = (m_used == ninf) ? 0.f : m_used;
 
+      // P row -> TMEM, packed two per column, over the first 64 columns of S_t.
       uint32_t pk[64];
-      float lsum = 0.f;
+      float ls0 = 0.f, ls1 = 0.f;
+      const float nm = -m_eff;
 #pragma unroll
       for (int c = 0; c < 128; c += 2) {
-        const float p0 = fast_exp2(fmaf(s[c], p.scale_log2, -m_eff));
-        const float p1 = fast_exp2(fmaf(s[c + 1], p.scale_log2, -m_eff));
-        lsum += p0 + p1;
+        float x0, x1;
+        fma2(x0, x1, s[c], s[c + 1], p.scale_log2, p.scale_log2, nm, nm);
+        const float p0 = fast_exp2(x0);
+        const float p1 = fast_exp2(x1);
+        add2(ls0, ls1, ls0, ls1, p0, p1);
         pk[c >> 1] = pack2<T>(p0, p1);
       }
-      l += lsum;
-
-      if (j > 0) {
-        // PV(j-1) must be complete before O is rescaled or P is overwritten.
-        ok = warp_wait(&o_done[t], (j - 1) & 1, wc, 10 + t, j);
-        if (!ok) break;
-        tc_fence_after();
-        if (resc_any) {
+      l += ls0 + ls1;
+      // PV(j-1) is complete here: S(j) was committed behind it on the in-order tensor pipe,
+      // so O may be rescaled and the P columns overwritten without another wait.
+      if (j > 0 && resc_any) {
 #pragma unroll
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t orr[32];
-            tmem_ld32(tmem_o + c * 32, orr);
-            tmem_ld_wait();
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t orr[32];
+          tmem_ld32(tmem_o + c * 32, orr);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i)
-              orr[i] = __float_as_uint(__uint_as_float(orr[i]) * alpha);
-            tmem_st32(tmem_o + c * 32, orr);
+          for (int i = 0; i < 32; i += 2) {
+            float y0, y1;
+            mul2(y0, y1, __uint_as_float(orr[i]), __uint_as_float(orr[i + 1]), alpha, alpha);
+            orr[i] = __float_as_uint(y0);
+            orr[i + 1] = __float_as_uint(y1);
           }
-          tmem_st_wait();
+          tmem_st32(tmem_o + c * 32, orr);
         }
       }
-      // P row -> TMEM, packed two per column, over the first 64 columns of S_t.
       tmem_st32(tmem_s, pk);
       tmem_st32(tmem_s + 32, pk + 32);
       tmem_st_wait();
