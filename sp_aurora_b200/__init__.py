@@ -46,6 +46,8 @@ from .hybrid import (  # noqa: F401
     set_seq_parallel_pg,
 )
 
+from .example_block import SequenceParallelAttentionBlock  # noqa: F401
+
 # Names used by the reference's README and tests for the ring entry points.
 sp_aurora_func = ring_flash_attn_func
 sp_aurora_kvpacked_func = ring_flash_attn_kvpacked_func

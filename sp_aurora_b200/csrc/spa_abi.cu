@@ -370,10 +370,13 @@ delta_kernel(const T* __restrict__ out, int64_t o_sb, int64_t o_ss, int64_t o_sh
   }
 }
 
-// merge: a warp takes 32 consecutive rows. Lane i first turns the two lse values of row i
-// into (lse', w_old, w_blk) -- the exponentials, the logarithm and the divisions are done
-// once per row, not once per element vector -- then the warp sweeps the rows, 128 floats
-// (32 lanes x float4) per pass, with the weights of each row broadcast by shuffles.
+// merge: a warp takes kMergeRows consecutive rows. Lane i (< kMergeRows) first turns the two
+// lse values of row i into (lse', w_old, w_blk) -- the exponentials, the logarithm and the
+// divisions are done once per row, not once per element vector -- then the warp sweeps the
+// rows, 128 floats (32 lanes x float4) per pass, with the weights of each row broadcast by
+// shuffles. Eight rows per warp keep the grid at several waves of equal blocks (with 32 the
+// cfg3 shard was 1.7 waves and the second one ran 27 % empty).
+constexpr int kMergeRows = 8;
 template <typename T, typename Idx>
 __global__ void __launch_bounds__(256)
 merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse, const T* __restrict__ bo,
@@ -382,11 +385,11 @@ merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse, const T* __re
   const int lane = threadIdx.x & 31;
   const Idx warp = ((Idx)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const Idx nrows = (Idx)B * S * H;
-  const Idx row0 = warp * 32;
+  const Idx row0 = warp * kMergeRows;
   if (row0 >= nrows) return;
   // phase 1: lane i owns row row0 + i
   const Idx my_row = row0 + lane;
-  const bool mine = my_row < nrows;
+  const bool mine = lane < kMergeRows && my_row < nrows;
   const RowIdx mr = decode_row<Idx>(mine ? my_row : 0, S, H);
   const size_t li = ((size_t)mr.b * H + mr.h) * S + mr.s;
   float w_old = 0.f, w_blk = 0.f;
@@ -407,7 +410,7 @@ merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse, const T* __re
   // phase 2: `rpp` rows per pass (a row is D/4 lanes wide), two passes in flight
   const int lpr = D / 4, rpp = 32 / lpr;
   const int sub = lane / lpr, c = (lane % lpr) * 4;
-  const int n = (int)min((Idx)32, nrows - row0);
+  const int n = (int)min((Idx)kMergeRows, nrows - row0);
   for (int i = 0; i < n; i += 2 * rpp) {
     float4 av[2], xv[2];
     float wo[2], wb[2];
@@ -416,7 +419,7 @@ merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse, const T* __re
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       rr[u] = i + u * rpp + sub;
-      const int src = min(rr[u], 31);
+      const int src = min(rr[u], kMergeRows - 1);
       wo[u] = __shfl_sync(0xffffffffu, w_old, src);
       wb[u] = __shfl_sync(0xffffffffu, w_blk, src);
       const long long off_lo = __shfl_sync(0xffffffffu, (long long)my_bo, src);
@@ -773,7 +776,7 @@ int spa_merge(float* out_acc, float* lse, const void* block_out, int64_t bo_sb, 
     set_error("spa_merge: out_acc must be 16-byte aligned, block_out base and strides multiples of 4 elements");
     return SPA_EINVAL;
   }
-  const long long threads = (long long)B * S * H;          // a warp per 32 rows: one thread per row
+  const long long threads = ((long long)B * S * H + kMergeRows - 1) / kMergeRows * 32;   // a warp per kMergeRows rows
   const int block = 256;
   const long long grid = (threads + block - 1) / block;
   const bool small = grid * block < (1ll << 31);

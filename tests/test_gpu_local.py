@@ -344,3 +344,35 @@ def test_bounded_wait_gives_up_and_reports(spa):
         spa.check_status()
     spa.check_status()                                   # the read cleared the word
     _check_fwd(spa, 1, 256, 256, 2, 2, 128, torch.bfloat16, True)
+
+
+def test_attention_block_matches_a_torch_reference(spa):
+    """QKV projection -> attention -> output projection (the reference's example model shape,
+    examples/example_mpi_integration.py:38-86) on one GPU, GQA, against the same block computed
+    with the CPU oracle between fp32 copies of the same projections; gradients of x included."""
+    torch.manual_seed(0)
+    B, S, d_model, hq, hkv = 1, 384, 512, 4, 2
+    D = d_model // hq
+    blk = spa.SequenceParallelAttentionBlock(d_model, hq, hkv, mode="ring", device="cuda")
+    x = (torch.randn(B, S, d_model) * 0.5).bfloat16()
+    dy = (torch.randn(B, S, d_model) * 0.5).bfloat16()
+    xc = x.cuda().requires_grad_(True)
+    y = blk(xc, causal=True)
+    y.backward(dy.cuda())
+    spa.check_status()
+    wq = blk.qkv_proj.weight.detach().cpu().double()
+    wo = blk.out_proj.weight.detach().cpu().double()
+    xr = x.double().requires_grad_(True)
+    qkv = (xr @ wq.t()).view(B, S, hq + 2 * hkv, D)
+    q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:]
+    g = hq // hkv
+    qt = q.permute(0, 2, 1, 3)
+    kt = k.permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    vt = v.permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
+    sc = torch.matmul(qt, kt.transpose(-2, -1)) * D ** -0.5
+    sc = sc.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool), diagonal=1), float("-inf"))
+    o = torch.matmul(torch.softmax(sc, -1), vt).permute(0, 2, 1, 3).reshape(B, S, d_model)
+    yr = o @ wo.t()
+    yr.backward(dy.double())
+    assert (y.detach().cpu().double() - yr.detach()).abs().max() <= 3e-2     # two bf16 GEMM roundings on top
+    assert (xc.grad.cpu().double() - xr.grad).abs().max() <= 3e-2 * max(1.0, float(xr.grad.abs().max()) / 4)
