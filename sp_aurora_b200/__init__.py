@@ -44,14 +44,25 @@ from .hybrid import (  # noqa: F401
     LongContextAttentionQKVPacked,
     destroy_seq_parallel_pg,
     set_seq_parallel_pg,
+    high_priority_nccl_options,
 )
 
 from .example_block import SequenceParallelAttentionBlock  # noqa: F401
+from .varlen import (  # noqa: F401
+    ring_flash_attn_varlen_func,
+    zigzag_ring_flash_attn_func,
+    zigzag_ring_flash_attn_varlen_func,
+)
 
 # Names used by the reference's README and tests for the ring entry points.
 sp_aurora_func = ring_flash_attn_func
 sp_aurora_kvpacked_func = ring_flash_attn_kvpacked_func
 sp_aurora_qkvpacked_func = ring_flash_attn_qkvpacked_func
+# Names the reference's varlen test imports
+# (test/flash_attention/test_intel_ring_flash_attn_varlen.py:23-26).
+sp_aurora_varlen_func = ring_flash_attn_varlen_func
+zigzag_sp_aurora_func = zigzag_ring_flash_attn_func
+zigzag_sp_aurora_varlen_func = zigzag_ring_flash_attn_varlen_func
 
 # The reference's own spellings (sp_aurora/intel_ring_flash_attn.py:453-456,
 # sp_aurora/intel_ulysses_attn.py:501-624, sp_aurora/__init__.py:59-72).

@@ -66,6 +66,28 @@ def seq_parallel_group_ranks(sp_ulysses_degree: int, sp_ring_degree: int, world_
     return ulysses, ring
 
 
+def high_priority_nccl_options():
+    """NCCL group options with high-priority streams, or None without the NCCL backend.
+
+    The attention kernels keep every SM occupied, so a send/recv kernel of default priority is
+    only scheduled once the attention kernel drains and the ring hop stops overlapping compute
+    (measured on 4 B200s: 4.2 ms of dk|dv waits per cfg4 step at default priority, 0.01 ms with
+    high-priority streams).  Pass the result as `pg_options` to `init_process_group` /
+    `new_group`; `set_seq_parallel_pg` does so for the groups it creates."""
+    if not (dist.is_available() and dist.is_nccl_available()):
+        return None
+    return dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+
+
+def _group_kwargs(backend: Optional[str]) -> dict:
+    effective = backend or (dist.get_backend() if dist.is_initialized() else "nccl")
+    if str(effective) == "nccl":
+        opts = high_priority_nccl_options()
+        if opts is not None:
+            return {"pg_options": opts}
+    return {}
+
+
 def set_seq_parallel_pg(sp_ulysses_degree: int, sp_ring_degree: int, rank: int, world_size: int,
                         backend: Optional[str] = None) -> None:
     """Create the Ulysses and ring groups; same signature and errors as
@@ -74,18 +96,18 @@ def set_seq_parallel_pg(sp_ulysses_degree: int, sp_ring_degree: int, rank: int, 
         raise ValueError("Process groups already initialized")
     ulysses, ring = seq_parallel_group_ranks(sp_ulysses_degree, sp_ring_degree, world_size)
     if not dist.is_initialized():
-        dist.init_process_group(backend=backend or "nccl")
+        dist.init_process_group(backend=backend or "nccl", **_group_kwargs(backend))
     PROCESS_GROUP._ulysses_degree = sp_ulysses_degree
     PROCESS_GROUP._ring_degree = sp_ring_degree
     PROCESS_GROUP._rank = rank
     PROCESS_GROUP._world_size = world_size
     # new_group is collective over the default group: every rank creates every group.
     for ranks in ulysses:
-        g = dist.new_group(ranks, backend=backend)
+        g = dist.new_group(ranks, backend=backend, **_group_kwargs(backend))
         if rank in ranks:
             PROCESS_GROUP.ULYSSES_PG = g
     for ranks in ring:
-        g = dist.new_group(ranks, backend=backend)
+        g = dist.new_group(ranks, backend=backend, **_group_kwargs(backend))
         if rank in ranks:
             PROCESS_GROUP.RING_PG = g
     PROCESS_GROUP.initialized = True

@@ -27,6 +27,32 @@ _SUPPORTED_D = (32, 64, 128)
 KERNEL_TIMERS = None
 
 
+# Optional per-stage timing of the multi-GPU schedules: when set to a dict, the ring code
+# brackets its stages (re-layout exchanges, per-step kernel groups, waits for transfers)
+# with CUDA events on the compute stream and appends (start, end) under the stage's name.
+# A "wait" stage is the time the compute stream stalls for a transfer, i.e. exposed
+# communication. None (default) records nothing.
+STAGE_TIMERS = None
+
+
+class stage:
+    def __init__(self, name, device):
+        self.name, self.device = name, device
+
+    def __enter__(self):
+        if STAGE_TIMERS is not None:
+            self.start = torch.cuda.Event(enable_timing=True)
+            self.end = torch.cuda.Event(enable_timing=True)
+            self.start.record(torch.cuda.current_stream(self.device))
+        return self
+
+    def __exit__(self, *exc):
+        if STAGE_TIMERS is not None:
+            self.end.record(torch.cuda.current_stream(self.device))
+            STAGE_TIMERS.setdefault(self.name, []).append((self.start, self.end))
+        return False
+
+
 class _Timed:
     def __init__(self, name, device, flops=0.0):
         self.name, self.device, self.flops = name, device, flops

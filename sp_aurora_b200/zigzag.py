@@ -157,10 +157,20 @@ def _stat_rows(s_z: torch.Tensor, lo: int, n: int) -> torch.Tensor:
     return s_z.view(B, Hq, 2 * h)
 
 
+def _local_relayout(pairs) -> None:
+    """The caller's shard already is in the zigzag layout: halves are copied, not exchanged."""
+    for src, dst in pairs:
+        for i in range(2):
+            dst[i].copy_(src[i])
+
+
 def zigzag_ring_forward(group, q, k, v, softmax_scale: float,
                         fwd_step: Callable = local_attn.attn_fwd_step,
-                        cast_fn: Callable = local_attn.cast_from_f32, need_lse: bool = True):
-    """Causal ring forward over contiguous shards with internal zigzag balance.
+                        cast_fn: Callable = local_attn.cast_from_f32, need_lse: bool = True,
+                        input_layout: str = "contiguous"):
+    """Causal ring forward with zigzag balance. `input_layout` "contiguous": rank r holds
+    chunk r, re-laid out internally (one exchange in, one out); "zigzag": the shard already
+    holds half-chunks r and 2W-1-r back to back and the result comes back in that layout.
     Returns (out [B,S,Hq,D], lse [B,Hq,S], saved) with `saved` = zigzag-layout
     tensors for the backward (q_z, kv_z, out_z, lse_z)."""
     from .ring import RingComm
@@ -172,11 +182,15 @@ def zigzag_ring_forward(group, q, k, v, softmax_scale: float,
         raise ValueError("the balanced causal ring needs an even local sequence length")
     h = S // 2
     dev, dt = q.device, q.dtype
+    stage = local_attn.stage
     q_z = torch.empty((2, B, h, Hq, D), dtype=dt, device=dev)
     kv_z = torch.empty((2, 2, B, h, Hkv, D), dtype=dt, device=dev)      # [k|v][half]
-    exchange_halves([(_halves(q), [q_z[0], q_z[1]]),
-                     (_halves(k), [kv_z[0, 0], kv_z[0, 1]]),
-                     (_halves(v), [kv_z[1, 0], kv_z[1, 1]])], group, to_zigzag=True)
+    relayout = exchange_halves if input_layout == "contiguous" else \
+        (lambda pairs, group, to_zigzag: _local_relayout(pairs))
+    with stage("fwd.relayout_in", dev):
+        relayout([(_halves(q), [q_z[0], q_z[1]]),
+                  (_halves(k), [kv_z[0, 0], kv_z[0, 1]]),
+                  (_halves(v), [kv_z[1, 0], kv_z[1, 1]])], group, to_zigzag=True)
 
     out_z = torch.empty((2, B, h, Hq, D), dtype=dt, device=dev)
     acc_z = torch.empty((2, B, h, Hq, D), dtype=torch.float32, device=dev)
@@ -192,20 +206,22 @@ def zigzag_ring_forward(group, q, k, v, softmax_scale: float,
         if step + 1 != W:
             nxt = comm.send_recv(cur, bufs[step % 2])
             comm.commit()
-        for q_lo, q_n, k_lo, k_n, causal, off in plan[step]:
-            halves = range(q_lo, q_lo + q_n)
-            first = done[q_lo] == 0                       # the same for every half of a call
-            last_any = any(done[i] + 1 == n_calls[i] for i in halves)
-            last_all = all(done[i] + 1 == n_calls[i] for i in halves)
-            fwd_step(_rows(q_z, q_lo, q_n), _rows(cur[0], k_lo, k_n), _rows(cur[1], k_lo, k_n),
-                     softmax_scale, causal, _stat_rows(lse_z, q_lo, q_n),
-                     out=_rows(out_z, q_lo, q_n) if last_any else None,
-                     out_acc=None if (first and last_all) else _rows(acc_z, q_lo, q_n),
-                     merge_prev=not first, causal_off=off * h)
-            for i in halves:
-                done[i] += 1
+        with stage("fwd.kernels", dev):
+            for q_lo, q_n, k_lo, k_n, causal, off in plan[step]:
+                halves = range(q_lo, q_lo + q_n)
+                first = done[q_lo] == 0                       # the same for every half of a call
+                last_any = any(done[i] + 1 == n_calls[i] for i in halves)
+                last_all = all(done[i] + 1 == n_calls[i] for i in halves)
+                fwd_step(_rows(q_z, q_lo, q_n), _rows(cur[0], k_lo, k_n), _rows(cur[1], k_lo, k_n),
+                         softmax_scale, causal, _stat_rows(lse_z, q_lo, q_n),
+                         out=_rows(out_z, q_lo, q_n) if last_any else None,
+                         out_acc=None if (first and last_all) else _rows(acc_z, q_lo, q_n),
+                         merge_prev=not first, causal_off=off * h)
+                for i in halves:
+                    done[i] += 1
         if nxt is not None:
-            comm.wait()
+            with stage("fwd.wait_kv", dev):
+                comm.wait()
             cur = nxt
 
     out = torch.empty((B, S, Hq, D), dtype=dt, device=dev)
@@ -215,7 +231,8 @@ def zigzag_ring_forward(group, q, k, v, softmax_scale: float,
         lse = torch.empty((B, Hq, S), dtype=torch.float32, device=dev)
         pairs.append(([lse_z[:, :, 0].contiguous(), lse_z[:, :, 1].contiguous()],
                       [lse[:, :, :h], lse[:, :, h:]]))
-    exchange_halves(pairs, group, to_zigzag=False)
+    with stage("fwd.relayout_out", dev):
+        relayout(pairs, group, to_zigzag=False)
     return out, lse, (q_z, kv_z, out_z, lse_z)
 
 
@@ -223,9 +240,9 @@ def zigzag_ring_backward(group, dout, q_z, kv_z, out_z, lse_z, softmax_scale: fl
                          bwd_step: Callable = local_attn.attn_bwd_step,
                          delta_fn: Callable = local_attn.bwd_delta,
                          cast_fn: Callable = local_attn.cast_from_f32,
-                         deterministic: bool = False):
-    """Backward of zigzag_ring_forward. `dout` is the contiguous shard; returns
-    (dq, dk, dv) as contiguous shards in q's dtype.
+                         deterministic: bool = False, input_layout: str = "contiguous"):
+    """Backward of zigzag_ring_forward. `dout` is the shard in the forward's `input_layout`;
+    returns (dq, dk, dv) as shards of the same layout in q's dtype.
 
     Each step runs its dQ passes first and its dK/dV passes second: the travelling dK|dV
     partial of the current block is still in flight during the dQ passes, and the dK/dV
@@ -238,15 +255,20 @@ def zigzag_ring_backward(group, dout, q_z, kv_z, out_z, lse_z, softmax_scale: fl
     Hkv = kv_z.shape[4]
     dev, dt = q_z.device, q_z.dtype
     DQ, DKV = _lib.SPA_BWD_DQ_ONLY, _lib.SPA_BWD_DKV_ONLY
+    stage = local_attn.stage
     do_z = torch.empty((2, B, h, Hq, D), dtype=dt, device=dev)
-    exchange_halves([(_halves(dout), [do_z[0], do_z[1]])], group, to_zigzag=True)
+    relayout = exchange_halves if input_layout == "contiguous" else \
+        (lambda pairs, group, to_zigzag: _local_relayout(pairs))
+    with stage("bwd.relayout_in", dev):
+        relayout([(_halves(dout), [do_z[0], do_z[1]])], group, to_zigzag=True)
     merged = B == 1
-    if merged:
-        delta_z = delta_fn(_rows(out_z, 0, 2), _rows(do_z, 0, 2)).view(B, Hq, 2, h)
-    else:
-        delta_z = torch.empty((B, Hq, 2, h), dtype=torch.float32, device=dev)
-        for i in range(2):
-            delta_z[:, :, i].copy_(delta_fn(out_z[i], do_z[i]))
+    with stage("bwd.delta", dev):
+        if merged:
+            delta_z = delta_fn(_rows(out_z, 0, 2), _rows(do_z, 0, 2)).view(B, Hq, 2, h)
+        else:
+            delta_z = torch.empty((B, Hq, 2, h), dtype=torch.float32, device=dev)
+            for i in range(2):
+                delta_z[:, :, i].copy_(delta_fn(out_z[i], do_z[i]))
     dq_acc = torch.empty((2, B, h, Hq, D), dtype=torch.float32, device=dev)
     dq_z = torch.empty((2, B, h, Hq, D), dtype=dt, device=dev)
     plan = [_plan(s, r, W, merged) for s in range(W)]
@@ -261,50 +283,57 @@ def zigzag_ring_backward(group, dout, q_z, kv_z, out_z, lse_z, softmax_scale: fl
         if step + 1 != W:
             nxt = kv_comm.send_recv(cur, kv_bufs[step % 2])
             kv_comm.commit()
-        for q_lo, q_n, k_lo, k_n, causal, off in plan[step]:
-            halves = range(q_lo, q_lo + q_n)
-            first = done[q_lo] == 0
-            last_any = any(done[i] + 1 == n_calls[i] for i in halves)
-            bwd_step(_rows(q_z, q_lo, q_n), _rows(cur[0], k_lo, k_n), _rows(cur[1], k_lo, k_n),
-                     _rows(do_z, q_lo, q_n), _stat_rows(lse_z, q_lo, q_n),
-                     _stat_rows(delta_z, q_lo, q_n), softmax_scale, causal,
-                     _rows(dq_acc, q_lo, q_n), None, None, causal_off=off * h,
-                     dq=_rows(dq_z, q_lo, q_n) if last_any else None, dq_overwrite=first,
-                     deterministic=deterministic, passes=DQ)
-            for i in halves:
-                done[i] += 1
+        with stage("bwd.dq_kernels", dev):
+            for q_lo, q_n, k_lo, k_n, causal, off in plan[step]:
+                halves = range(q_lo, q_lo + q_n)
+                first = done[q_lo] == 0
+                last_any = any(done[i] + 1 == n_calls[i] for i in halves)
+                bwd_step(_rows(q_z, q_lo, q_n), _rows(cur[0], k_lo, k_n), _rows(cur[1], k_lo, k_n),
+                         _rows(do_z, q_lo, q_n), _stat_rows(lse_z, q_lo, q_n),
+                         _stat_rows(delta_z, q_lo, q_n), softmax_scale, causal,
+                         _rows(dq_acc, q_lo, q_n), None, None, causal_off=off * h,
+                         dq=_rows(dq_z, q_lo, q_n) if last_any else None, dq_overwrite=first,
+                         deterministic=deterministic, passes=DQ)
+                for i in halves:
+                    done[i] += 1
         tgt = dkv_bufs[step % 2]
         if step > 0:
-            d_kv_comm.wait()           # the partial that travels with this block has arrived in tgt
+            with stage("bwd.wait_dkv", dev):
+                d_kv_comm.wait()       # the partial that travels with this block has arrived in tgt
         written = [step > 0, step > 0]
-        for q_lo, q_n, k_lo, k_n, causal, off in plan[step]:
-            khalves = range(k_lo, k_lo + k_n)
-            bwd_step(_rows(q_z, q_lo, q_n), _rows(cur[0], k_lo, k_n), _rows(cur[1], k_lo, k_n),
-                     _rows(do_z, q_lo, q_n), _stat_rows(lse_z, q_lo, q_n),
-                     _stat_rows(delta_z, q_lo, q_n), softmax_scale, causal,
-                     None, _rows(tgt[0], k_lo, k_n), _rows(tgt[1], k_lo, k_n),
-                     dkv_accumulate=written[k_lo], causal_off=off * h,
-                     deterministic=deterministic, passes=DKV)
-            for i in khalves:
-                written[i] = True
+        with stage("bwd.dkv_kernels", dev):
+            for q_lo, q_n, k_lo, k_n, causal, off in plan[step]:
+                khalves = range(k_lo, k_lo + k_n)
+                bwd_step(_rows(q_z, q_lo, q_n), _rows(cur[0], k_lo, k_n), _rows(cur[1], k_lo, k_n),
+                         _rows(do_z, q_lo, q_n), _stat_rows(lse_z, q_lo, q_n),
+                         _stat_rows(delta_z, q_lo, q_n), softmax_scale, causal,
+                         None, _rows(tgt[0], k_lo, k_n), _rows(tgt[1], k_lo, k_n),
+                         dkv_accumulate=written[k_lo], causal_off=off * h,
+                         deterministic=deterministic, passes=DKV)
+                for i in khalves:
+                    written[i] = True
         if nxt is not None:
-            kv_comm.wait()
+            with stage("bwd.wait_kv", dev):
+                kv_comm.wait()
             cur = nxt
         d_kv_comm.send_recv(tgt, dkv_bufs[(step + 1) % 2])
         d_kv_comm.commit()
-    d_kv_comm.wait()
+    with stage("bwd.wait_last_dkv_hop", dev):
+        d_kv_comm.wait()
     home = dkv_bufs[W % 2]
 
     def to_dt(x):  # fp32 [B,h,H,D] -> dt
         return x if dt == torch.float32 else cast_fn(x, dt)
 
-    dk_h = [to_dt(home[0, i]) for i in range(2)]
-    dv_h = [to_dt(home[1, i]) for i in range(2)]
+    with stage("bwd.cast_dkv", dev):
+        dk_h = [to_dt(home[0, i]) for i in range(2)]
+        dv_h = [to_dt(home[1, i]) for i in range(2)]
     S = 2 * h
     dq = torch.empty((B, S, Hq, D), dtype=dt, device=dev)
     dk = torch.empty((B, S, Hkv, D), dtype=dt, device=dev)
     dv = torch.empty((B, S, Hkv, D), dtype=dt, device=dev)
-    exchange_halves([([dq_z[0], dq_z[1]], [dq[:, :h], dq[:, h:]]),
-                     (dk_h, [dk[:, :h], dk[:, h:]]),
-                     (dv_h, [dv[:, :h], dv[:, h:]])], group, to_zigzag=False)
+    with stage("bwd.relayout_out", dev):
+        relayout([([dq_z[0], dq_z[1]], [dq[:, :h], dq[:, h:]]),
+                  (dk_h, [dk[:, :h], dk[:, h:]]),
+                  (dv_h, [dv[:, :h], dv[:, h:]])], group, to_zigzag=False)
     return dq, dk, dv

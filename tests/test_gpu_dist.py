@@ -39,7 +39,9 @@ def _worker(rank, world, port, ret):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    from sp_aurora_b200 import high_priority_nccl_options
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            pg_options=high_priority_nccl_options())
     res = {}
     try:
         import sp_aurora_b200 as spa
@@ -190,6 +192,52 @@ def _worker(rank, world, port, ret):
             all(d <= 2e-2 * (gmax if i >= 2 else 1.0) for i, d in enumerate(pair_diffs) if i != 1)
         res["world_size_independence"] = (ok, diffs + pair_diffs, 0.0)
 
+        # ---- public zigzag layout and packed variable-length sequences over the ring
+        H, D = 4, 128
+        lengths = [512 * world // 2, 256 * world // 2 * 2, 128 * world]      # global lengths, multiples of 2*world
+        gq, gk, gv, gdo = ([_rand((1, L, H, D), 60 + 10 * t + i).bfloat16() for i, L in enumerate(lengths)]
+                           for t in range(4))
+        refs = []
+        for i in range(len(lengths)):
+            ro, rl = orc.attention_ref(gq[i], gk[i], gv[i], None, True, dtype=torch.float32)
+            refs.append((ro, rl) + orc.attention_bwd_ref(gdo[i], gq[i], gk[i], gv[i], ro, rl, None, True,
+                                                         dtype=torch.float32))
+        worst = [0.0] * 5
+        for layout in ("contiguous", "zigzag"):
+            def shard(x):
+                L = x.shape[1]
+                if layout == "contiguous":
+                    return x[0, rank * (L // world):(rank + 1) * (L // world)]
+                hc = L // (2 * world)
+                return torch.cat((x[0, rank * hc:(rank + 1) * hc],
+                                  x[0, (2 * world - 1 - rank) * hc:(2 * world - rank) * hc]))
+            ql, kl, vl, dol = (torch.cat([shard(x) for x in g]).to(dev) for g in (gq, gk, gv, gdo))
+            ql, kl, vl = (t.requires_grad_(True) for t in (ql, kl, vl))
+            cu = torch.tensor([0] + list(torch.tensor([L // world for L in lengths]).cumsum(0)),
+                              dtype=torch.int32, device=dev)
+            fn = spa.sp_aurora_varlen_func if layout == "contiguous" else spa.zigzag_sp_aurora_varlen_func
+            out, lse, _ = fn(ql, kl, vl, cu, cu, max_seqlen=max(lengths) // world, causal=True,
+                             return_attn_probs=True)
+            out.backward(dol)
+            spa.check_status()
+            for i in range(len(lengths)):
+                sl = slice(int(cu[i]), int(cu[i + 1]))
+                want = [shard(r) if r.dim() == 4 else None for r in refs[i]]
+                lse_ref = refs[i][1]
+                Lg = lengths[i]
+                if layout == "contiguous":
+                    lw = lse_ref[0, :, rank * (Lg // world):(rank + 1) * (Lg // world)]
+                else:
+                    hc = Lg // (2 * world)
+                    lw = torch.cat((lse_ref[0, :, rank * hc:(rank + 1) * hc],
+                                    lse_ref[0, :, (2 * world - 1 - rank) * hc:(2 * world - rank) * hc]), dim=1)
+                e = _errs([(out[sl], want[0]), (lse[:, sl], lw), (ql.grad[sl], want[2]), (kl.grad[sl], want[3]),
+                           (vl.grad[sl], want[4])])
+                worst = [max(a, b) for a, b in zip(worst, e)]
+        gmax = max(1.0, max(float(r[4].abs().max()) for r in refs) / 4)
+        res["varlen_and_zigzag_layout"] = (worst[0] <= 2e-2 and worst[1] <= 1e-3 and max(worst[2:]) <= 2e-2 * gmax,
+                                           worst, worst[1])
+
         # ---- BASELINE cfg2 at its stated size: bf16 B1 S=32768 H32 D128 causal over all ranks;
         # 64-row slices of out / lse / dq per rank against the oracle, dk / dv of the last 64
         # keys on the last rank, and the two checksum identities for dk / dv of every key
@@ -255,7 +303,8 @@ def results():
 
 @pytest.mark.parametrize("tag", ["ring_fp32", "ring_bf16_gqa", "ring_bf16_gqa_contig", "ring_bf16_noncausal", "uly_b2",
                                  "uly_gqa_causal", "a2a_exact", "hyb_u", "hyb_r", "hyb_bwd", "hyb_u4r2",
-                                 "run_twice_bitwise", "world_size_independence", "cfg2_full_size"])
+                                 "run_twice_bitwise", "world_size_independence", "varlen_and_zigzag_layout",
+                                 "cfg2_full_size"])
 def test_multi_gpu_parity(results, tag, error_log):
     for r, res in results.items():
         ok, errs, el = res[tag]

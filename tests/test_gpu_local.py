@@ -376,3 +376,33 @@ def test_attention_block_matches_a_torch_reference(spa):
     yr.backward(dy.double())
     assert (y.detach().cpu().double() - yr.detach()).abs().max() <= 3e-2     # two bf16 GEMM roundings on top
     assert (xc.grad.cpu().double() - xr.grad).abs().max() <= 3e-2 * max(1.0, float(xr.grad.abs().max()) / 4)
+
+
+@pytest.mark.parametrize("lengths", [[128, 256, 128], [100, 100, 100, 100], [512], [64, 128, 256, 512]])
+def test_varlen_packed_sequences(spa, lengths):
+    """Packed variable-length sequences (the shapes of the reference's
+    test/flash_attention/test_intel_ring_flash_attn_varlen.py:37-77: fp16, 8 heads, D=64, causal),
+    forward and backward, each sequence against the oracle; the zigzag variant on one rank is the
+    same computation."""
+    H, D = 8, 64
+    total = sum(lengths)
+    cu = torch.tensor([0] + list(torch.tensor(lengths).cumsum(0)), dtype=torch.int32)
+    q, k, v, do = (_rand((total, H, D), torch.float16, s_) for s_ in (31, 32, 33, 34))
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out, lse, _ = spa.sp_aurora_varlen_func(qc, kc, vc, cu.cuda(), cu.cuda(), max_seqlen=max(lengths),
+                                            dropout_p=0.0, causal=True, return_attn_probs=True)
+    assert out.shape == (total, H, D) and lse.shape == (H, total)
+    out.backward(do.cuda())
+    out2 = spa.zigzag_sp_aurora_varlen_func(qc.detach(), kc.detach(), vc.detach(), cu.cuda(), cu.cuda(),
+                                            max_seqlen=max(lengths), causal=True)
+    spa.check_status()
+    assert torch.equal(out2, out.detach())
+    for i in range(len(lengths)):
+        sl = slice(int(cu[i]), int(cu[i + 1]))
+        ro, rl = orc.attention_ref(q[None, sl], k[None, sl], v[None, sl], None, True)
+        rdq, rdk, rdv = orc.attention_bwd_ref(do[None, sl], q[None, sl], k[None, sl], v[None, sl], ro, rl,
+                                              None, True)
+        assert (out[sl].detach().cpu().double() - ro[0]).abs().max() <= 2e-2
+        assert (lse[:, sl].cpu().double() - rl[0]).abs().max() <= 1e-3
+        for got, want in ((qc.grad[sl], rdq[0]), (kc.grad[sl], rdk[0]), (vc.grad[sl], rdv[0])):
+            assert (got.cpu().double() - want).abs().max() <= grad_tol(torch.float16, want)

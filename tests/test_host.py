@@ -140,6 +140,23 @@ def _zigzag_errs(rank, world, orc):
             float((dq.double() - fdq[:, sli]).abs().max()),
             float((dk.double() - fdk[:, sli]).abs().max()),
             float((dv.double() - fdv[:, sli]).abs().max())]
+        # the same problem with the shards handed over in the zigzag layout (half-chunks r and
+        # 2W-1-r back to back): no re-layout exchange, results come back in that layout
+        hc = S // (2 * world)
+        rows = torch.cat((torch.arange(rank * hc, (rank + 1) * hc),
+                          torch.arange((2 * world - 1 - rank) * hc, (2 * world - rank) * hc)))
+        qs, ks, vs, ds = (t[:, rows].contiguous() for t in (q, k, v, dout))
+        out, lse, saved = zigzag.zigzag_ring_forward(None, qs, ks, vs, D ** -0.5, fwd_step=orc.fwd_step_cpu,
+                                                     cast_fn=orc.cast_cpu, input_layout="zigzag")
+        dq, dk, dv = zigzag.zigzag_ring_backward(None, ds, *saved, D ** -0.5, bwd_step=orc.bwd_step_cpu,
+                                                 delta_fn=orc.delta_cpu, cast_fn=orc.cast_cpu,
+                                                 input_layout="zigzag")
+        errs[(hq, hkv, B, "zigzag-in")] = [
+            float((out.double() - full_out[:, rows]).abs().max()),
+            float((lse.double() - full_lse[:, :, rows]).abs().max()),
+            float((dq.double() - fdq[:, rows]).abs().max()),
+            float((dk.double() - fdk[:, rows]).abs().max()),
+            float((dv.double() - fdv[:, rows]).abs().max())]
     return errs
 
 
