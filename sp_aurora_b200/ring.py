@@ -213,13 +213,18 @@ def ring_flash_attn_backward(process_group, dout, q, k, v, out, softmax_lse, sof
         if nxt is not None:
             kv_comm.wait()
             cur = nxt
-        d_kv_comm.send_recv(tgt, dkv_bufs[(step + 1) % 2])
-        d_kv_comm.commit()
+        if step + 1 != W:
+            d_kv_comm.send_recv(tgt, dkv_bufs[(step + 1) % 2])
+            d_kv_comm.commit()
+    # The block now here has every rank's share: it goes home in the element type (the rounding
+    # its owner would apply, half the bytes of the fp32 partial).
+    done = dkv_bufs[(W - 1) % 2]
+    if q.dtype != torch.float32:
+        done = cast_fn(done.view(2 * B, S, Hkv, D), q.dtype).view(2, B, S, Hkv, D)
+    home = d_kv_comm.send_recv(done)
+    d_kv_comm.commit()
     d_kv_comm.wait()
-    home = dkv_bufs[W % 2]
-    if q.dtype == torch.float32:
-        return dq, home[0], home[1]
-    return dq, cast_fn(home[0], q.dtype), cast_fn(home[1], q.dtype)
+    return dq, home[0], home[1]
 
 
 def _use_zigzag(group, q, causal) -> bool:

@@ -45,22 +45,28 @@ def half_owner(c: int, W: int) -> Tuple[int, int]:
 
 
 def exchange_halves(pairs: Sequence[Tuple[List[torch.Tensor], List[torch.Tensor]]], group,
-                    to_zigzag: bool) -> None:
+                    to_zigzag: bool, shift: int = 0, defer: bool = False):
     """Move half-chunks between the contiguous layout (rank r holds half-chunks
-    2r, 2r+1) and the zigzag layout (rank r holds r, 2W-1-r).
+    2r, 2r+1) and the zigzag layout (rank r holds the pair b, 2W-1-b of block
+    b = (r - shift) mod W; shift = 0 is the resting layout, shift = s is where a block
+    sits after s ring hops).
 
     `pairs` is a list of (src_halves, dst_halves): two tensors each; sources must be
     contiguous, destinations may be strided views (received through a staging tensor).
     to_zigzag=True : src_halves[i] is half-chunk 2r+i, dst_halves[j] receives slot j.
     to_zigzag=False: src_halves[j] is slot j, dst_halves[i] receives half-chunk 2r+i.
-    All transfers of all pairs go out as one batched group (ordered per peer)."""
+    All transfers of all pairs go out as one batched group (ordered per peer).
+    With defer=True the transfers are posted and a function is returned that makes the
+    current stream wait for them (and finishes staged copies); otherwise that happens
+    before returning."""
     from .ring import RingComm
     if RingComm.FAKE:          # measurement aid: local copies only, no transfers
         for src, dst in pairs:
             for i in range(2):
                 dst[i].copy_(src[i])
-        return
+        return (lambda: None) if defer else None
     r, W = _group_info(group)
+    blk = (r - shift) % W      # the block whose pair this rank holds in the zigzag layout
     ops = []
     local = []       # (dst, src) copies that can run at once
     after = []       # (dst, staging) copies that wait for their receive
@@ -75,7 +81,8 @@ def exchange_halves(pairs: Sequence[Tuple[List[torch.Tensor], List[torch.Tensor]
     for src, dst in pairs:
         for i in range(2):
             c = 2 * r + i                      # half-chunk living here in contiguous layout
-            zr, zs = half_owner(c, W)          # where it lives in zigzag layout
+            zb, zs = half_owner(c, W)          # its block and slot in the zigzag layout
+            zr = (zb + shift) % W              # the rank holding that block
             if to_zigzag:
                 if zr == r:
                     local.append((dst[zs], src[i]))
@@ -87,10 +94,10 @@ def exchange_halves(pairs: Sequence[Tuple[List[torch.Tensor], List[torch.Tensor]
                 else:
                     recv_into(dst[i], zr)
         for j in range(2):
-            c = r if j == 0 else 2 * W - 1 - r  # half-chunk living here in zigzag layout
-            cr = c // 2                         # its rank in contiguous layout
+            c = blk if j == 0 else 2 * W - 1 - blk   # half-chunk living here in zigzag layout
+            cr = c // 2                              # its rank in contiguous layout
             if cr == r:
-                continue                        # handled as a local copy above
+                continue                             # handled as a local copy above
             if to_zigzag:
                 recv_into(dst[j], cr)
             else:
@@ -98,10 +105,16 @@ def exchange_halves(pairs: Sequence[Tuple[List[torch.Tensor], List[torch.Tensor]
     reqs = dist.batch_isend_irecv(ops) if ops else []
     for d, s in local:
         d.copy_(s)
-    for req in reqs:
-        req.wait()
-    for d, s in after:
-        d.copy_(s)
+
+    def finish():
+        for req in reqs:
+            req.wait()
+        for d, s in after:
+            d.copy_(s)
+
+    if defer:
+        return finish
+    finish()
 
 
 def _halves(x: torch.Tensor) -> List[torch.Tensor]:
@@ -157,11 +170,37 @@ def _stat_rows(s_z: torch.Tensor, lo: int, n: int) -> torch.Tensor:
     return s_z.view(B, Hq, 2 * h)
 
 
-def _local_relayout(pairs) -> None:
-    """The caller's shard already is in the zigzag layout: halves are copied, not exchanged."""
-    for src, dst in pairs:
-        for i in range(2):
-            dst[i].copy_(src[i])
+def _zigzag_layout_relayout(pairs, group, to_zigzag: bool, shift: int = 0, defer: bool = False):
+    """exchange_halves for a caller whose shard already is in the zigzag layout: halves
+    at rest are copied; a block that sits `shift` hops from home is sent there."""
+    from .ring import RingComm
+    r, W = _group_info(group)
+    reqs, after = [], []
+    if shift % W and not RingComm.FAKE:
+        ops = []
+        for src, dst in pairs:
+            for j in range(2):
+                tgt = dst[j]
+                if not tgt.is_contiguous():
+                    tgt = torch.empty(tgt.shape, dtype=tgt.dtype, device=tgt.device)
+                    after.append((dst[j], tgt))
+                ops.append(dist.P2POp(dist.isend, src[j], _global(group, (r - shift) % W), group=group))
+                ops.append(dist.P2POp(dist.irecv, tgt, _global(group, (r + shift) % W), group=group))
+        reqs = dist.batch_isend_irecv(ops)
+    else:
+        for src, dst in pairs:
+            for i in range(2):
+                dst[i].copy_(src[i])
+
+    def finish():
+        for req in reqs:
+            req.wait()
+        for d, s in after:
+            d.copy_(s)
+
+    if defer:
+        return finish
+    finish()
 
 
 def zigzag_ring_forward(group, q, k, v, softmax_scale: float,
@@ -185,8 +224,7 @@ def zigzag_ring_forward(group, q, k, v, softmax_scale: float,
     stage = local_attn.stage
     q_z = torch.empty((2, B, h, Hq, D), dtype=dt, device=dev)
     kv_z = torch.empty((2, 2, B, h, Hkv, D), dtype=dt, device=dev)      # [k|v][half]
-    relayout = exchange_halves if input_layout == "contiguous" else \
-        (lambda pairs, group, to_zigzag: _local_relayout(pairs))
+    relayout = exchange_halves if input_layout == "contiguous" else _zigzag_layout_relayout
     with stage("fwd.relayout_in", dev):
         relayout([(_halves(q), [q_z[0], q_z[1]]),
                   (_halves(k), [kv_z[0, 0], kv_z[0, 1]]),
@@ -257,8 +295,7 @@ def zigzag_ring_backward(group, dout, q_z, kv_z, out_z, lse_z, softmax_scale: fl
     DQ, DKV = _lib.SPA_BWD_DQ_ONLY, _lib.SPA_BWD_DKV_ONLY
     stage = local_attn.stage
     do_z = torch.empty((2, B, h, Hq, D), dtype=dt, device=dev)
-    relayout = exchange_halves if input_layout == "contiguous" else \
-        (lambda pairs, group, to_zigzag: _local_relayout(pairs))
+    relayout = exchange_halves if input_layout == "contiguous" else _zigzag_layout_relayout
     with stage("bwd.relayout_in", dev):
         relayout([(_halves(dout), [do_z[0], do_z[1]])], group, to_zigzag=True)
     merged = B == 1
@@ -277,6 +314,11 @@ def zigzag_ring_backward(group, dout, q_z, kv_z, out_z, lse_z, softmax_scale: fl
     # fp32 travelling partials [2(k|v), 2(half), B, h, Hkv, D], one message
     dkv_bufs = [torch.empty((2, 2, B, h, Hkv, D), dtype=torch.float32, device=dev) for _ in range(2)]
     kv_bufs = [torch.empty_like(kv_z), torch.empty_like(kv_z)]
+    S = 2 * h
+    dq = torch.empty((B, S, Hq, D), dtype=dt, device=dev)
+    dk = torch.empty((B, S, Hkv, D), dtype=dt, device=dev)
+    dv = torch.empty((B, S, Hkv, D), dtype=dt, device=dev)
+    finish_dq = None
     cur = kv_z
     for step in range(W):
         nxt = None
@@ -296,6 +338,11 @@ def zigzag_ring_backward(group, dout, q_z, kv_z, out_z, lse_z, softmax_scale: fl
                          deterministic=deterministic, passes=DQ)
                 for i in halves:
                     done[i] += 1
+        if step + 1 == W:
+            # dq is complete: its way back to the contiguous layout overlaps the last dK/dV pass
+            with stage("bwd.relayout_out", dev):
+                finish_dq = relayout([([dq_z[0], dq_z[1]], [dq[:, :h], dq[:, h:]])], group,
+                                     to_zigzag=False, defer=True)
         tgt = dkv_bufs[step % 2]
         if step > 0:
             with stage("bwd.wait_dkv", dev):
@@ -316,24 +363,22 @@ def zigzag_ring_backward(group, dout, q_z, kv_z, out_z, lse_z, softmax_scale: fl
             with stage("bwd.wait_kv", dev):
                 kv_comm.wait()
             cur = nxt
-        d_kv_comm.send_recv(tgt, dkv_bufs[(step + 1) % 2])
-        d_kv_comm.commit()
-    with stage("bwd.wait_last_dkv_hop", dev):
-        d_kv_comm.wait()
-    home = dkv_bufs[W % 2]
+        if step + 1 != W:
+            d_kv_comm.send_recv(tgt, dkv_bufs[(step + 1) % 2])
+            d_kv_comm.commit()
 
-    def to_dt(x):  # fp32 [B,h,H,D] -> dt
-        return x if dt == torch.float32 else cast_fn(x, dt)
-
+    # The block now here has collected every rank's share.  It leaves in the element type
+    # (the same rounding the owner would apply, half the bytes) and, for contiguous shards,
+    # goes straight to the ranks that own its two halves instead of home first.
     with stage("bwd.cast_dkv", dev):
-        dk_h = [to_dt(home[0, i]) for i in range(2)]
-        dv_h = [to_dt(home[1, i]) for i in range(2)]
-    S = 2 * h
-    dq = torch.empty((B, S, Hq, D), dtype=dt, device=dev)
-    dk = torch.empty((B, S, Hkv, D), dtype=dt, device=dev)
-    dv = torch.empty((B, S, Hkv, D), dtype=dt, device=dev)
+        done_dkv = dkv_bufs[(W - 1) % 2]
+        msg = done_dkv
+        if dt != torch.float32:
+            msg = cast_fn(done_dkv.view(4 * B, h, Hkv, D), dt).view(2, 2, B, h, Hkv, D)
+    with stage("bwd.wait_last_dkv_hop", dev):
+        relayout([([msg[0, 0], msg[0, 1]], [dk[:, :h], dk[:, h:]]),
+                  ([msg[1, 0], msg[1, 1]], [dv[:, :h], dv[:, h:]])], group,
+                 to_zigzag=False, shift=W - 1)
     with stage("bwd.relayout_out", dev):
-        relayout([([dq_z[0], dq_z[1]], [dq[:, :h], dq[:, h:]]),
-                  (dk_h, [dk[:, :h], dk[:, h:]]),
-                  (dv_h, [dv[:, :h], dv[:, h:]])], group, to_zigzag=False)
+        finish_dq()
     return dq, dk, dv

@@ -294,11 +294,14 @@ def test_gloo_zigzag_ring_two_ranks(gloo_results):
             assert max(errs) < 2e-5, (r, key, errs)
 
 
-def test_gloo_zigzag_ring_four_ranks():
+@pytest.mark.parametrize("world", [3, 4])
+def test_gloo_zigzag_ring_more_ranks(world):
+    """Odd and even ring sizes: with W = 3 both halves of one rank's shard come from the same
+    peer on the last dK|dV hop, which is the case where per-peer message order matters."""
     mgr = mp.Manager()
     ret = mgr.dict()
-    mp.spawn(_worker4, args=(4, _free_port(), ret), nprocs=4, join=True)
-    for r in range(4):
+    mp.spawn(_worker4, args=(world, _free_port(), ret), nprocs=world, join=True)
+    for r in range(world):
         res = dict(ret[r])
         assert "error" not in res, res.get("error")
         for key, errs in res["zigzag_errs"].items():
