@@ -48,6 +48,13 @@ from .hybrid import (  # noqa: F401
 )
 
 from .example_block import SequenceParallelAttentionBlock  # noqa: F401
+from .mpi_utils import (  # noqa: F401
+    cleanup_distributed,
+    detect_mpi_environment,
+    get_device_for_rank,
+    init_distributed_backend,
+    setup_mpi_distributed,
+)
 from .varlen import (  # noqa: F401
     ring_flash_attn_varlen_func,
     zigzag_ring_flash_attn_func,
