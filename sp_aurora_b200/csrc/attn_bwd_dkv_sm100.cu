@@ -167,11 +167,11 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(p_full, kComputeThreads);
-    mbar_init(ds_full, kComputeThreads);
+    mbar_init(p_full, kComputeThreads / 32);
+    mbar_init(ds_full, kComputeThreads / 32);
     mbar_init(mma_done, 1);
-    for (int i = 0; i < kStatBufs; ++i) mbar_init(&row_ready[i], 256);
-    mbar_init(epi_full, kComputeThreads);
+    for (int i = 0; i < kStatBufs; ++i) mbar_init(&row_ready[i], 256 / 32);
+    mbar_init(epi_full, kComputeThreads / 32);
     fence_mbar_init();
     fence_proxy_async_smem();
   }
@@ -328,7 +328,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     };
     if (n_it > 0 && stat_tid < 256) {
       row_buf[(0 * 2 + (stat_tid >> 7)) * kTileQ + (stat_tid & 127)] = fetch_rowstat(0);
-      mbar_arrive(&row_ready[0]);
+      warp_arrive(&row_ready[0]);
     }
 
     for (int it = 0; it < n_it; ++it) {
@@ -402,7 +402,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       tmem_st_16x128b_x4(t_s + half_step, pk + 8);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(p_full);
+      warp_arrive(p_full);
 
       float2 dl[4];
 #pragma unroll
@@ -433,10 +433,10 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       tmem_st_wait();
       if (stat_tid < 256 && it + 1 < n_it) {
         row_buf[(((it + 1) % kStatBufs) * 2 + (stat_tid >> 7)) * kTileQ + (stat_tid & 127)] = next_stat;
-        mbar_arrive(&row_ready[(it + 1) % kStatBufs]);
+        warp_arrive(&row_ready[(it + 1) % kStatBufs]);
       }
       tc_fence_before();
-      mbar_arrive(ds_full);
+      warp_arrive(ds_full);
     }
 
     if (ok && n_it > 0) {
@@ -483,7 +483,7 @@ attn_bwd_dkv_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
         }
       }
       fence_proxy_async_smem();
-      mbar_arrive(epi_full);
+      warp_arrive(epi_full);
       if (threadIdx.x == 0) {
         bool go = mbar_wait(epi_full, 0, wc, 12, 0);
         go = go && !*cta_abort && !(p.q_split > 1 && n_it == 0);

@@ -138,14 +138,14 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
   if (threadIdx.x == 0) {
     *cta_abort = 0;
     mbar_init(do_full, 1);
-    mbar_init(q_ready, kComputeThreads);
+    mbar_init(q_ready, kComputeThreads / 32);
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(sdp_free, kComputeThreads);
-    mbar_init(ds_full, kComputeThreads);
+    mbar_init(sdp_free, kComputeThreads / 32);
+    mbar_init(ds_full, kComputeThreads / 32);
     mbar_init(dq_done, 1);
     fence_mbar_init();
     fence_proxy_async_smem();
@@ -286,7 +286,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
       if constexpr (D == 128) tmem_st16(t_q, qw); else tmem_st8(t_q, qw);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(q_ready);
+      warp_arrive(q_ready);
     }
     // Row statistics, negated for the packed multiply-adds: -inf in place of -lse makes
     // out-of-range rows give P = 0.
@@ -306,7 +306,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
       tmem_ld32(t_dp, dpr);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(sdp_free);
+      warp_arrive(sdp_free);
       float* pr = reinterpret_cast<float*>(sr);   // scores, then probabilities, in place
 
       const int k0 = j * kTileN;
@@ -350,7 +350,7 @@ attn_bwd_dq_sm100_kernel(const __grid_constant__ CUtensorMap tm_k,
       tmem_st16(t_ds, dsp);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(ds_full);
+      warp_arrive(ds_full);
     }
 
     // ------------------------------------------------------------- epilogue

@@ -143,7 +143,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
     }
     for (int t = 0; t < 2; ++t) {
       mbar_init(&s_full[t], 1);
-      mbar_init(&p_full[t], 128);
+      mbar_init(&p_full[t], 128 / 32);
       mbar_init(&o_done[t], 1);
     }
     fence_mbar_init();
@@ -349,7 +349,7 @@ attn_fwd_sm100_kernel(const __grid_constant__ CUtensorMap tm_q,
       tmem_st32(tmem_s + 32, pk + 32);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&p_full[t]);
+      warp_arrive(&p_full[t]);
     }
 
     // ------------------------------------------------------------- epilogue

@@ -35,6 +35,15 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// One arrival for a whole warp: the lanes' earlier writes (TMEM stores completed by
+// tcgen05.wait::st, shared-memory stores) are ordered before lane 0's releasing arrive by
+// the warp barrier. 32 lanes arriving one by one on the same word keep the shared-memory
+// pipe busy for tens of cycles per warp; barriers that compute warps arrive on count warps.
+// Every lane of the warp must reach the call.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                "r"(bytes)
