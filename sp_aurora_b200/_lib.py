@@ -119,7 +119,7 @@ def _rebuild_if_stale() -> str:
     try:
         stale = _build._stale(_LIB_PATH, [_build.CSRC / s for s in _build.SOURCES] + _build.HEADERS)
         if stale:
-            _build.build()
+            _build.build()      # serialised across processes by a file lock; re-checks staleness
     except RuntimeError as e:
         return str(e)
     return ""

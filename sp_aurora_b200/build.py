@@ -45,7 +45,22 @@ def _stale(target: Path, deps) -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile (if stale) and return the path of the shared library."""
+    """Compile (if stale) and return the path of the shared library. Safe to call from several
+    processes at once (one rank per GPU importing the package): an exclusive file lock lets one
+    of them build while the others wait and then find the library fresh; the library itself is
+    replaced atomically."""
+    import fcntl
+    obj_dir = PKG_DIR / "build"
+    obj_dir.mkdir(exist_ok=True)
+    with open(obj_dir / ".lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            return _build_locked(force, verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(force: bool, verbose: bool) -> Path:
     nvcc = _nvcc()
     flags = [f for f in NVCC_FLAGS if not f.startswith("--use_fast_math")]
     obj_dir = PKG_DIR / "build"
@@ -72,13 +87,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             list(ex.map(compile_one, jobs))
     objs = [obj_dir / (src + ".o") for src in SOURCES]
     if force or jobs or _stale(LIB_PATH, objs):
+        tmp = LIB_PATH.with_name(f"{LIB_PATH.name}.{os.getpid()}.tmp")
         cmd = [nvcc, "-shared", "-cudart", "static", "-gencode", "arch=compute_100a,code=sm_100a",
-               "-o", str(LIB_PATH), *map(str, objs)]
+               "-o", str(tmp), *map(str, objs)]
         if verbose:
             print(" ".join(cmd), flush=True)
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+        os.replace(tmp, LIB_PATH)
     return LIB_PATH
 
 
