@@ -314,7 +314,7 @@ def run_hybrid(args, rank, world, device, steps, warmup):
     sl = S // world
     lo = rank * sl
     qkv = gen_rows(888, 0, Bw, lo, lo + sl, (3, H, D)).to(device)
-    U = min(4, world)
+    U = min(args.ulysses_degree or 4, world)
     while world % U:
         U -= 1
     if world > 1:
@@ -517,6 +517,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the cfg3 / cfg5 workloads and the serial e2e")
     ap.add_argument("--workload", default="ring", choices=["ring", "ulysses", "hybrid", "block"])
+    ap.add_argument("--ulysses-degree", type=int, default=0,
+                    help="--workload hybrid: Ulysses degree (default min(4, N)); the ring takes the rest")
     ap.add_argument("--aux", action="store_true", help="bandwidth of the HBM-bound helper kernels")
     ap.add_argument("--aux-batch", type=int, default=2, help="batch of the --aux tensors (16 = 1 GiB)")
     ap.add_argument("--aux-iters", type=int, default=20)
@@ -543,10 +545,7 @@ def main():
         # High-priority NCCL streams: the attention grids keep every SM busy, and a transfer
         # kernel of default priority would only be scheduled when the attention kernel ends
         # (SPA_NCCL_HIGH_PRIORITY=0 restores the default for an A/B).
-        opts = None
-        if os.environ.get("SPA_NCCL_HIGH_PRIORITY", "1") != "0":
-            opts = spa.high_priority_nccl_options()
-        dist.init_process_group("nccl", device_id=device, pg_options=opts)
+        dist.init_process_group("nccl", device_id=device, pg_options=spa.high_priority_nccl_options())
 
     if args.workload != "ring":
         fn = {"ulysses": run_ulysses, "hybrid": run_hybrid, "block": run_block}[args.workload]
@@ -779,11 +778,11 @@ def main():
     if not args.no_extra and args.seq == DEFAULT_SEQ:
         del q, kv, dout
         torch.cuda.empty_cache()
-        extra["cfg3_ulysses"] = run_ulysses(args, rank, world, device, 3, 3)
+        extra["cfg3_ulysses"] = run_ulysses(args, rank, world, device, 5, 4)
         torch.cuda.empty_cache()
-        extra["cfg5_hybrid"] = run_hybrid(args, rank, world, device, 3, 3)
+        extra["cfg5_hybrid"] = run_hybrid(args, rank, world, device, 5, 4)
         torch.cuda.empty_cache()
-        extra["attention_block"] = run_block(args, rank, world, device, 3, 3)
+        extra["attention_block"] = run_block(args, rank, world, device, 5, 4)
 
     total_flops = 3.5 * fwd_flops(args.seq)
     value = total_flops / (ms * 1e-3) / 1e12

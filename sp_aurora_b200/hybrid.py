@@ -73,7 +73,11 @@ def high_priority_nccl_options():
     only scheduled once the attention kernel drains and the ring hop stops overlapping compute
     (measured on 4 B200s: 4.2 ms of dk|dv waits per cfg4 step at default priority, 0.01 ms with
     high-priority streams).  Pass the result as `pg_options` to `init_process_group` /
-    `new_group`; `set_seq_parallel_pg` does so for the groups it creates."""
+    `new_group`; `set_seq_parallel_pg` does so for the groups it creates.
+    SPA_NCCL_HIGH_PRIORITY=0 makes this return None (default-priority streams)."""
+    import os
+    if os.environ.get("SPA_NCCL_HIGH_PRIORITY", "1") == "0":
+        return None
     if not (dist.is_available() and dist.is_nccl_available()):
         return None
     return dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)

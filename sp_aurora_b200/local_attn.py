@@ -329,9 +329,26 @@ def update_out_and_lse(out: Optional[torch.Tensor], lse: Optional[torch.Tensor],
     Counterpart of sp_aurora/utils.py:109 update_out_and_lse with this package's
     layouts: out fp32 [B,S,H,D], lse fp32 [B,H,S], block_out [B,S,H,D] (any
     supported dtype), block_lse [B,H,S]. The first call (out is None) returns
-    fp32 copies (sp_aurora/utils.py:116-122); later calls update in place."""
+    fp32 copies (sp_aurora/utils.py:116-122); later calls update in place.
+
+    `slice_` (sp_aurora/utils.py:123-128, used by zigzag-style callers that merge a block into
+    part of the rows): a `slice` over the sequence dimension; the block is merged into
+    out[:, slice_] and lse[:, :, slice_]. The reference indexes its [B,H,S,D] accumulator with
+    a tuple; with this package's layouts out and lse order their dimensions differently, so
+    only the sequence range is taken."""
     if slice_ is not None:
-        raise NotImplementedError("slice_ is only used by the varlen/zigzag variants")
+        if out is None:
+            raise RuntimeError("first update_out_and_lse should not pass slice_ args")
+        if isinstance(slice_, tuple):          # (..., seq_slice): keep the last entry
+            slice_ = slice_[-1]
+        if not isinstance(slice_, slice):
+            raise ValueError("slice_ must be a slice over the sequence dimension")
+        sub_out = out[:, slice_].contiguous()
+        sub_lse = lse[:, :, slice_].contiguous()
+        update_out_and_lse(sub_out, sub_lse, block_out, block_lse)
+        out[:, slice_].copy_(sub_out)
+        lse[:, :, slice_].copy_(sub_lse)
+        return out, lse
     _check_tensor("block_out", block_out)
     B, S, H, D = block_out.shape
     if tuple(block_lse.shape) != (B, H, S):

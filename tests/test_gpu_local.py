@@ -170,6 +170,19 @@ def test_golden_fixtures_on_gpu(spa, golden_dir):
     out, lse = spa.update_out_and_lse(out, lse, o2, l2)
     assert (out.cpu() - torch.from_numpy(gd["m_out"])).abs().max() <= 1e-5
     assert (lse.cpu() - torch.from_numpy(gd["m_lse"])).abs().max() <= 1e-5
+    # slice_ (sp_aurora/utils.py:123-128): the second block merged into a row range only
+    S = o1.shape[1]
+    sl = slice(S // 4, S // 2)
+    out_s, lse_s = spa.update_out_and_lse(None, None, o1, l1)
+    keep_o, keep_l = out_s.clone(), lse_s.clone()
+    out_s, lse_s = spa.update_out_and_lse(out_s, lse_s, o2[:, sl].contiguous(), l2[:, :, sl].contiguous(),
+                                          slice_=sl)
+    assert torch.equal(out_s[:, sl], out[:, sl]) and torch.equal(lse_s[:, :, sl], lse[:, :, sl])
+    rest = torch.ones(S, dtype=torch.bool)
+    rest[sl] = False
+    assert torch.equal(out_s[:, rest], keep_o[:, rest]) and torch.equal(lse_s[:, :, rest], keep_l[:, :, rest])
+    with pytest.raises(RuntimeError):
+        spa.update_out_and_lse(None, None, o1, l1, slice_=sl)
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
