@@ -48,6 +48,16 @@ from .hybrid import (  # noqa: F401
 )
 
 from .example_block import SequenceParallelAttentionBlock  # noqa: F401
+from .llama3_varlen import (  # noqa: F401
+    llama3_flash_attn_prepare_cu_seqlens,
+    llama3_flash_attn_varlen_func,
+)
+from .adapters import (  # noqa: F401
+    substitute_hf_flash_attn,
+    update_ring_flash_attn_params,
+    update_sp_aurora_params,
+    use_ring_attn,
+)
 from .mpi_utils import (  # noqa: F401
     cleanup_distributed,
     detect_mpi_environment,

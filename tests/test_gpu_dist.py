@@ -238,6 +238,33 @@ def _worker(rank, world, port, ret):
         res["varlen_and_zigzag_layout"] = (worst[0] <= 2e-2 and worst[1] <= 1e-3 and max(worst[2:]) <= 2e-2 * gmax,
                                            worst, worst[1])
 
+        # ---- packed stream split evenly over the ranks (llama3-style: all-gather K/V, sequences
+        # straddling rank boundaries), GQA, kv heads gathered two at a time, bf16, fwd + bwd
+        T, hq, hkv, D = 1024 * world, 8, 4, 128
+        cu = [0, 300, 300 + 640 * world, T - 200, T]
+        gens = [torch.Generator().manual_seed(1200 + i) for i in range(4)]
+        qg, dog = (torch.randn(T, hq, D, generator=g).bfloat16() for g in (gens[0], gens[3]))
+        kg, vg = (torch.randn(T, hkv, D, generator=g).bfloat16() for g in gens[1:3])
+        ro, rl = torch.zeros(T, hq, D), torch.zeros(hq, T)
+        rdq, rdk, rdv = torch.zeros(T, hq, D), torch.zeros(T, hkv, D), torch.zeros(T, hkv, D)
+        for s0, s1 in zip(cu, cu[1:]):
+            ss = slice(s0, s1)
+            o, l = orc.attention_ref(qg[None, ss], kg[None, ss], vg[None, ss], None, True, dtype=torch.float32)
+            a, b_, c = orc.attention_bwd_ref(dog[None, ss], qg[None, ss], kg[None, ss], vg[None, ss], o, l,
+                                             None, True, dtype=torch.float32)
+            ro[ss], rl[:, ss], rdq[ss], rdk[ss], rdv[ss] = o[0], l[0], a[0], b_[0], c[0]
+        mine = slice(rank * (T // world), (rank + 1) * (T // world))
+        ql, kl, vl = (t[mine].to(dev).requires_grad_(True) for t in (qg, kg, vg))
+        cq, ck, mq, mk, ks = spa.llama3_flash_attn_prepare_cu_seqlens(cu, True, rank, world)
+        out, lse, _ = spa.llama3_flash_attn_varlen_func(ql, kl, vl, cq, ck, mq, mk, heads_k_stride=2,
+                                                        local_k_slice=ks, causal=True, return_attn_probs=True)
+        out.backward(dog[mine].to(dev))
+        spa.check_status()
+        e = _errs([(out, ro[mine]), (lse, rl[:, mine]), (ql.grad, rdq[mine]), (kl.grad, rdk[mine]),
+                   (vl.grad, rdv[mine])])
+        gmax = max(1.0, float(max(rdq.abs().max(), rdk.abs().max(), rdv.abs().max())) / 4)
+        res["llama3_packed_stream"] = (e[0] <= 2e-2 and e[1] <= 1e-3 and max(e[2:]) <= 2e-2 * gmax, e, e[1])
+
         # ---- BASELINE cfg2 at its stated size: bf16 B1 S=32768 H32 D128 causal over all ranks;
         # 64-row slices of out / lse / dq per rank against the oracle, dk / dv of the last 64
         # keys on the last rank, and the two checksum identities for dk / dv of every key
@@ -304,7 +331,7 @@ def results():
 @pytest.mark.parametrize("tag", ["ring_fp32", "ring_bf16_gqa", "ring_bf16_gqa_contig", "ring_bf16_noncausal", "uly_b2",
                                  "uly_gqa_causal", "a2a_exact", "hyb_u", "hyb_r", "hyb_bwd", "hyb_u4r2",
                                  "run_twice_bitwise", "world_size_independence", "varlen_and_zigzag_layout",
-                                 "cfg2_full_size"])
+                                 "llama3_packed_stream", "cfg2_full_size"])
 def test_multi_gpu_parity(results, tag, error_log):
     for r, res in results.items():
         ok, errs, el = res[tag]

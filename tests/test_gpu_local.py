@@ -419,3 +419,37 @@ def test_varlen_packed_sequences(spa, lengths):
         assert (lse[:, sl].cpu().double() - rl[0]).abs().max() <= 1e-3
         for got, want in ((qc.grad[sl], rdq[0]), (kc.grad[sl], rdk[0]), (vc.grad[sl], rdv[0])):
             assert (got.cpu().double() - want).abs().max() <= grad_tol(torch.float16, want)
+
+
+@pytest.mark.gpu
+def test_llama3_packed_stream_one_rank(spa):
+    """llama3_flash_attn_varlen_func on one rank (the all-gather is the identity): GQA, kv heads
+    two at a time, bf16, sequences of ragged lengths, forward and backward vs the oracle; strided
+    out / lse / dq views and fp32 dK/dV buffers are what the multi-rank path uses too."""
+    lengths = [300, 1, 515, 0, 208]
+    H, Hkv, D = 8, 4, 128
+    T = sum(lengths)
+    cu = [0]
+    for n in lengths:
+        cu.append(cu[-1] + n)
+    q, do = (_rand((T, H, D), torch.bfloat16, s_) for s_ in (41, 44))
+    k, v = (_rand((T, Hkv, D), torch.bfloat16, s_) for s_ in (42, 43))
+    qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    cq, ck, mq, mk, ks = spa.llama3_flash_attn_prepare_cu_seqlens(cu, True, 0, 1)
+    assert ks == slice(0, T) and mq == 515
+    out, lse, _ = spa.llama3_flash_attn_varlen_func(qc, kc, vc, cq, ck, mq, mk, heads_k_stride=2,
+                                                    local_k_slice=ks, causal=True, return_attn_probs=True)
+    out.backward(do.cuda())
+    spa.check_status()
+    assert out.shape == (T, H, D) and lse.shape == (H, T)
+    for a, b in zip(cu, cu[1:]):
+        if a == b:
+            continue
+        sl = slice(a, b)
+        ro, rl = orc.attention_ref(q[None, sl], k[None, sl], v[None, sl], None, True)
+        rdq, rdk, rdv = orc.attention_bwd_ref(do[None, sl], q[None, sl], k[None, sl], v[None, sl], ro, rl,
+                                              None, True)
+        assert (out[sl].detach().cpu().double() - ro[0]).abs().max() <= 2e-2
+        assert (lse[:, sl].cpu().double() - rl[0]).abs().max() <= 1e-3
+        for got, want in ((qc.grad[sl], rdq[0]), (kc.grad[sl], rdk[0]), (vc.grad[sl], rdv[0])):
+            assert (got.cpu().double() - want).abs().max() <= grad_tol(torch.bfloat16, want)
