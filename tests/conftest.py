@@ -19,14 +19,15 @@ def golden_dir():
 
 @pytest.fixture(scope="session")
 def error_log():
-    """Measured max-abs errors of the GPU parity cases, written to
-    gpurun_out/parity_errors.json at the end of the session (and printed with -s)."""
+    """Measured max-abs errors of the GPU parity cases, printed at the end of the session
+    (visible with -s) and written to $SPA_ARTIFACT_DIR/parity_errors.json when that is set."""
     import json
     log = {}
     yield log
     if log:
-        out_dir = os.path.join(ROOT, "gpurun_out")
-        os.makedirs(out_dir, exist_ok=True)
-        with open(os.path.join(out_dir, "parity_errors.json"), "w") as f:
-            json.dump(log, f, indent=1, sort_keys=True)
+        out_dir = os.environ.get("SPA_ARTIFACT_DIR")
+        if out_dir:
+            os.makedirs(out_dir, exist_ok=True)
+            with open(os.path.join(out_dir, "parity_errors.json"), "w") as f:
+                json.dump(log, f, indent=1, sort_keys=True)
         print("\nparity errors:", json.dumps(log, sort_keys=True))
