@@ -333,9 +333,12 @@ __device__ __forceinline__ float dot8<__half>(const Vec8<__half>& a, const Vec8<
   return acc;
 }
 
-// delta: one thread per 8 elements, D/8 consecutive threads share a row; kRowsInFlight rows
-// per thread with every load issued before the first use (the row of a thread in pass u is
-// its first row + u * rows-per-pass, so every pass is coalesced).
+// delta: one thread per 8 elements, D/8 consecutive lanes share a row. A warp takes
+// kRowsInFlight * (32 / (D/8)) consecutive sequence positions of one (batch, head): every load
+// is issued before the first use, and the row sums are gathered into the low lanes so that the
+// warp writes its part of delta ([B,H,S]) as one contiguous run instead of one 4-byte store
+// per sector. Consecutive warps take consecutive heads: the rows a block reads at one sequence
+// position are adjacent in memory.
 constexpr int kRowsInFlight = 4;
 
 template <typename T, typename Idx>
@@ -343,39 +346,50 @@ __global__ void __launch_bounds__(256)
 delta_kernel(const T* __restrict__ out, int64_t o_sb, int64_t o_ss, int64_t o_sh,
              const T* __restrict__ dout, int64_t d_sb, int64_t d_ss, int64_t d_sh,
              float* __restrict__ delta, int B, int S, int H, int D) {
-  const int tpr = D / 8;
-  const Idx nrows = (Idx)B * S * H;
-  const Idx rows_per_pass = ((Idx)gridDim.x * blockDim.x) / (Idx)tpr;
-  const Idx gid = (Idx)blockIdx.x * blockDim.x + threadIdx.x;
-  const int c = (int)(gid % (Idx)tpr) * 8;
-  Vec8<T> a[kRowsInFlight], b[kRowsInFlight];
-  size_t di[kRowsInFlight];
+  const int tpr = D / 8;                 // lanes per row: 4, 8 or 16
+  const int rpw = 32 / tpr;              // rows per warp and pass
+  const int sblk = kRowsInFlight * rpw;  // sequence positions per warp
+  const int lane = threadIdx.x & 31;
+  const Idx warp = ((Idx)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const Idx nsb = (Idx)((S + sblk - 1) / sblk);
+  if (warp >= (Idx)B * nsb * (Idx)H) return;
+  const int h = (int)(warp % (Idx)H);
+  const Idx t = warp / (Idx)H;
+  const int s0 = (int)(t % nsb) * sblk;
+  const int b = (int)(t / nsb);
+  const int sub = lane / tpr, c = (lane % tpr) * 8;
+  const T* o0 = out + (int64_t)b * o_sb + (int64_t)h * o_sh + c;
+  const T* d0 = dout + (int64_t)b * d_sb + (int64_t)h * d_sh + c;
+  Vec8<T> va[kRowsInFlight], vb[kRowsInFlight];
   bool ok[kRowsInFlight];
 #pragma unroll
   for (int u = 0; u < kRowsInFlight; ++u) {
-    const Idx row = gid / (Idx)tpr + (Idx)u * rows_per_pass;
-    ok[u] = row < nrows;
-    const RowIdx r = decode_row<Idx>(ok[u] ? row : 0, S, H);
-    di[u] = ((size_t)r.b * H + r.h) * S + r.s;
+    const int sq = s0 + u * rpw + sub;
+    ok[u] = sq < S;
     if (ok[u]) {
-      a[u] = load8<T>(out + r.b * o_sb + r.s * o_ss + r.h * o_sh + c);
-      b[u] = load8<T>(dout + r.b * d_sb + r.s * d_ss + r.h * d_sh + c);
+      va[u] = load8<T>(o0 + (int64_t)sq * o_ss);
+      vb[u] = load8<T>(d0 + (int64_t)sq * d_ss);
     }
   }
+  float res = 0.f;
 #pragma unroll
   for (int u = 0; u < kRowsInFlight; ++u) {
-    float acc = ok[u] ? dot8<T>(a[u], b[u]) : 0.f;
+    float acc = ok[u] ? dot8<T>(va[u], vb[u]) : 0.f;
     for (int o = tpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (ok[u] && c == 0) delta[di[u]] = acc;
+    // lane L of the low `sblk` lanes keeps the sum of position L = u * rpw + sub
+    const float v = __shfl_sync(0xffffffffu, acc, (lane % rpw) * tpr);
+    if (lane / rpw == u) res = v;
   }
+  if (lane < sblk && s0 + lane < S) delta[((size_t)b * H + h) * S + s0 + lane] = res;
 }
 
-// merge: a warp takes kMergeRows consecutive rows. Lane i (< kMergeRows) first turns the two
-// lse values of row i into (lse', w_old, w_blk) -- the exponentials, the logarithm and the
-// divisions are done once per row, not once per element vector -- then the warp sweeps the
-// rows, 128 floats (32 lanes x float4) per pass, with the weights of each row broadcast by
-// shuffles. Eight rows per warp keep the grid at several waves of equal blocks (with 32 the
-// cfg3 shard was 1.7 waves and the second one ran 27 % empty).
+// merge: a warp takes kMergeRows consecutive sequence positions of one (batch, head). Lane i
+// (< kMergeRows) first turns the two lse values of position i into (lse', w_old, w_blk) -- the
+// exponentials, the logarithm and the divisions are done once per row, not once per element
+// vector, and the lse values of a warp are one contiguous 32-byte sector ([B,H,S] layout) --
+// then the warp sweeps its rows, 128 floats (32 lanes x float4) per pass, with the weights of
+// each row broadcast by shuffles. Consecutive warps take consecutive heads, so the rows a block
+// touches at one sequence position are adjacent in memory.
 constexpr int kMergeRows = 8;
 template <typename T, typename Idx>
 __global__ void __launch_bounds__(256)
@@ -384,14 +398,16 @@ merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse, const T* __re
              int S, int H, int D) {
   const int lane = threadIdx.x & 31;
   const Idx warp = ((Idx)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-  const Idx nrows = (Idx)B * S * H;
-  const Idx row0 = warp * kMergeRows;
-  if (row0 >= nrows) return;
-  // phase 1: lane i owns row row0 + i
-  const Idx my_row = row0 + lane;
-  const bool mine = lane < kMergeRows && my_row < nrows;
-  const RowIdx mr = decode_row<Idx>(mine ? my_row : 0, S, H);
-  const size_t li = ((size_t)mr.b * H + mr.h) * S + mr.s;
+  const Idx nsb = (Idx)((S + kMergeRows - 1) / kMergeRows);
+  if (warp >= (Idx)B * nsb * (Idx)H) return;
+  const int h = (int)(warp % (Idx)H);
+  const Idx t = warp / (Idx)H;
+  const int s0 = (int)(t % nsb) * kMergeRows;
+  const int b = (int)(t / nsb);
+  const int n = min(kMergeRows, S - s0);
+  // phase 1: lane i owns sequence position s0 + i
+  const bool mine = lane < n;
+  const size_t li = ((size_t)b * H + h) * S + s0 + (mine ? lane : 0);
   float w_old = 0.f, w_blk = 0.f;
   if (mine) {
     const float lo = lse[li], lb = blse[li];
@@ -406,11 +422,12 @@ merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse, const T* __re
     }
     lse[li] = lse_new;
   }
-  const int64_t my_bo = mr.b * bo_sb + mr.s * bo_ss + mr.h * bo_sh;   // element offset of my row in bo
+  float* acc0 = out_acc + (((size_t)b * S + s0) * H + h) * D;          // row r: + r * H * D
+  const T* bo0 = bo + (int64_t)b * bo_sb + (int64_t)s0 * bo_ss + (int64_t)h * bo_sh;   // row r: + r * bo_ss
+  const size_t acc_step = (size_t)H * D;
   // phase 2: `rpp` rows per pass (a row is D/4 lanes wide), two passes in flight
   const int lpr = D / 4, rpp = 32 / lpr;
   const int sub = lane / lpr, c = (lane % lpr) * 4;
-  const int n = (int)min((Idx)kMergeRows, nrows - row0);
   for (int i = 0; i < n; i += 2 * rpp) {
     float4 av[2], xv[2];
     float wo[2], wb[2];
@@ -422,17 +439,16 @@ merge_kernel(float* __restrict__ out_acc, float* __restrict__ lse, const T* __re
       const int src = min(rr[u], kMergeRows - 1);
       wo[u] = __shfl_sync(0xffffffffu, w_old, src);
       wb[u] = __shfl_sync(0xffffffffu, w_blk, src);
-      const long long off_lo = __shfl_sync(0xffffffffu, (long long)my_bo, src);
       ok[u] = rr[u] < n;
       if (ok[u]) {
-        av[u] = __ldcs(reinterpret_cast<const float4*>(out_acc + (size_t)(row0 + rr[u]) * D + c));
-        xv[u] = ld4<T>(bo + off_lo + c);
+        av[u] = __ldcs(reinterpret_cast<const float4*>(acc0 + rr[u] * acc_step + c));
+        xv[u] = ld4<T>(bo0 + (int64_t)rr[u] * bo_ss + c);
       }
     }
 #pragma unroll
     for (int u = 0; u < 2; ++u)
       if (ok[u])
-        __stcs(reinterpret_cast<float4*>(out_acc + (size_t)(row0 + rr[u]) * D + c),
+        __stcs(reinterpret_cast<float4*>(acc0 + rr[u] * acc_step + c),
                make_float4(wo[u] * av[u].x + wb[u] * xv[u].x, wo[u] * av[u].y + wb[u] * xv[u].y,
                            wo[u] * av[u].z + wb[u] * xv[u].z, wo[u] * av[u].w + wb[u] * xv[u].w));
   }
@@ -749,10 +765,11 @@ int spa_bwd_delta(const void* out, int64_t o_sb, int64_t o_ss, int64_t o_sh, con
       return SPA_EINVAL;
     }
   }
-  const long long threads = ((long long)B * S * H + kRowsInFlight - 1) / kRowsInFlight * (D / 8);
-  const int block = 256;   // a multiple of D/8: rows never straddle blocks or passes
+  const int sblk = kRowsInFlight * (32 / (D / 8));                        // positions per warp
+  const long long threads = (long long)B * ((S + sblk - 1) / sblk) * H * 32;
+  const int block = 256;
   const long long grid = (threads + block - 1) / block;
-  const bool small = grid * block * kRowsInFlight < (1ll << 31);
+  const bool small = grid * block < (1ll << 31);
   SPA_DISPATCH_T(dtype, if (small) delta_kernel<T, uint32_t><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
                             (const T*)out, o_sb, o_ss, o_sh, (const T*)dout, do_sb, do_ss, do_sh,
                             delta, B, S, H, D);
@@ -776,7 +793,7 @@ int spa_merge(float* out_acc, float* lse, const void* block_out, int64_t bo_sb, 
     set_error("spa_merge: out_acc must be 16-byte aligned, block_out base and strides multiples of 4 elements");
     return SPA_EINVAL;
   }
-  const long long threads = ((long long)B * S * H + kMergeRows - 1) / kMergeRows * 32;   // a warp per kMergeRows rows
+  const long long threads = (long long)B * ((S + kMergeRows - 1) / kMergeRows) * H * 32;   // a warp per kMergeRows positions of a (b, h)
   const int block = 256;
   const long long grid = (threads + block - 1) / block;
   const bool small = grid * block < (1ll << 31);
