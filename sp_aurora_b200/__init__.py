@@ -109,3 +109,46 @@ def is_available() -> bool:
 
 
 __version__ = "0.1.0"
+
+
+# yunchang-style names the reference also exports (sp_aurora/kernels/attention.py:12-117,
+# sp_aurora/ring_pytorch_attn.py:20-240, sp_aurora/__init__.py:75). They are the same CUDA path
+# under the other spelling, not a PyTorch implementation.
+SeqAllToAll4D_v2 = SeqAllToAll4D
+
+
+def pytorch_attn_forward(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False,
+                         window_size=(-1, -1), softcap=0.0, alibi_slopes=None, deterministic=False,
+                         return_attn_probs=False):
+    """Single-device attention on [B, S, H, D] tensors: (out, lse or None). The reference
+    returns the S x S probability matrix with `return_attn_probs`; here the second value is the
+    fp32 log-sum-exp [B, H, S], which is what the ring and hybrid callers consume."""
+    from .local_attn import LocalFlashAttnFunc, check_unsupported_kwargs
+    check_unsupported_kwargs(dropout_p, window_size, alibi_slopes, softcap)
+    out, lse = LocalFlashAttnFunc.apply(q, k, v, softmax_scale, causal)
+    return out, (lse if return_attn_probs else None)
+
+
+def pytorch_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False, window_size=(-1, -1),
+                      softcap=0.0, alibi_slopes=None, deterministic=False, return_attn_probs=False):
+    return pytorch_attn_forward(q, k, v, dropout_p, softmax_scale, causal, window_size, softcap,
+                                alibi_slopes, deterministic, False)[0]
+
+
+def ring_pytorch_attn_func(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False,
+                           window_size=(-1, -1), alibi_slopes=None, deterministic=False,
+                           return_attn_probs=False, group=None):
+    return ring_flash_attn_func(q, k, v, dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal,
+                                window_size=window_size, alibi_slopes=alibi_slopes,
+                                deterministic=deterministic, return_attn_probs=return_attn_probs,
+                                group=group)
+
+
+def ring_pytorch_attn_forward(q, k, v, dropout_p=0.0, softmax_scale=None, causal=False,
+                              window_size=(-1, -1), alibi_slopes=None, deterministic=False,
+                              return_attn_probs=False, group=None):
+    """(out, lse): the reference's version returns None for lse (sp_aurora/ring_pytorch_attn.py:236)."""
+    res = ring_flash_attn_func(q, k, v, dropout_p=dropout_p, softmax_scale=softmax_scale, causal=causal,
+                               window_size=window_size, alibi_slopes=alibi_slopes,
+                               deterministic=deterministic, return_attn_probs=True, group=group)
+    return res[0], res[1]

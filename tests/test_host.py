@@ -360,8 +360,16 @@ def test_reference_export_names_exist():
                  "intel_ring_flash_attn_func", "intel_ring_flash_attn_kvpacked_func",
                  "intel_ring_flash_attn_qkvpacked_func", "IntelRingFlashAttnFunc",
                  "intel_ulysses_flash_attn_func", "sp_aurora_func", "sp_aurora_kvpacked_func",
-                 "sp_aurora_qkvpacked_func"):
+                 "sp_aurora_qkvpacked_func", "SeqAllToAll4D_v2", "pytorch_attn_forward", "pytorch_attn_func",
+                 "ring_pytorch_attn_func", "ring_pytorch_attn_forward", "substitute_hf_flash_attn",
+                 "update_sp_aurora_params", "setup_mpi_distributed", "init_distributed_backend",
+                 "cleanup_distributed", "get_device_for_rank", "detect_mpi_environment"):
         assert hasattr(spa, name), name
+    # CPU tensors are refused loudly: there is no PyTorch fallback behind the yunchang-style names
+    import torch
+    x = torch.zeros(1, 8, 2, 32)
+    with pytest.raises(ValueError):
+        spa.pytorch_attn_func(x, x, x)
     comm = spa.UlyssesComm(None)
     assert comm.world_size == 1 and comm.rank == 0
     assert spa.HAS_SPARSE_SAGE_ATTENTION is False
