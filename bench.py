@@ -184,7 +184,8 @@ def cpu_reference_sample(seq=4096, steps=1, threads=None):
 
 def run_aux(args):
     """`--aux`: achieved HBM bandwidth of the bandwidth-bound helper kernels
-    (Ulysses pack/unpack permutation, stand-alone merge, delta, fp32->bf16 cast) on
+    (Ulysses pack/unpack permutation, the pack with rotary embedding, stand-alone merge, delta,
+    fp32->bf16 cast) on
     cfg3-sized tensors, against the measured copy bandwidth. One JSON line."""
     import sp_aurora_b200 as spa
     from sp_aurora_b200 import all_to_all as a2a, local_attn as la
@@ -202,6 +203,8 @@ def run_aux(args):
     blse = torch.randn(Bq, H, S, device="cuda")
     nbytes = x.numel() * 2
     rows = Bq * S * H
+    from sp_aurora_b200 import rope as rope_mod
+    cos, sin = rope_mod.rope_tables(S, Dh, device="cuda")
 
     def timeit(fn, n=args.aux_iters):
         for _ in range(3):
@@ -218,6 +221,8 @@ def run_aux(args):
     res = {}
     for name, fn, traffic in (
             ("permute_rows pack (seq->head, 256 B rows)", lambda: a2a.strided_copy(send, src), 2 * nbytes),
+            ("rope + pack (rotary embedding fused into the seq->head pack)",
+             lambda: rope_mod.rope_copy(send, src, cos, sin, 2, 0), 2 * nbytes),
             ("permute_rows unpack (head->seq)", lambda: a2a.strided_copy(outp.view(Bq, S, P, H // P, Dh),
                                                                           send.permute(1, 2, 0, 3, 4)), 2 * nbytes),
             ("merge (fp32 acc r/w + bf16 block + 3 lse)", lambda: la.update_out_and_lse(acc, lse, x, blse),

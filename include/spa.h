@@ -229,6 +229,21 @@ int spa_permute_rows(const void* src, void* dst, const int64_t n[4], const int64
                      const int64_t dst_stride[4], int64_t row_bytes, void* stream);
 
 /*
+ * Rotary position embedding fused into the same kind of strided row copy (no counterpart in the
+ * reference: its example block, examples/example_mpi_integration.py:38-86, applies no position
+ * embedding; a caller with RoPE would otherwise pay one more full pass over q and k before the
+ * Ulysses pack of sp_aurora/intel_ulysses_attn.py:95-110).
+ * Logical array [n0,n1,n2,n3] of head rows of D elements; strides in ELEMENTS per logical dim
+ * (multiples of 16 bytes); dst[:D/2] = x1*cos - x2*sin, dst[D/2:] = x2*cos + x1*sin ("rotate
+ * half"), cos/sin fp32 [table_rows, D/2] indexed by pos_offset + index along logical dim
+ * pos_dim. inverse != 0 negates sin (the gradient of the rotation). src == dst is allowed.
+ */
+int spa_rope_rows(const void* src, void* dst, const int64_t n[4], const int64_t src_stride[4],
+                  const int64_t dst_stride[4], int32_t D, int32_t dtype, const float* cos_table,
+                  const float* sin_table, int64_t table_rows, int32_t pos_dim, int64_t pos_offset,
+                  int32_t inverse, void* stream);
+
+/*
  * Device facts. Replaces sp_aurora/sycl_bindings/bindings.cpp:298 get_device_info_py
  * and :362 is_available. Fills: [0] SM count, [1] cc major, [2] cc minor,
  * [3] max opt-in shared memory per block, [4] L2 bytes, [5] global memory MiB.

@@ -58,6 +58,7 @@ from .adapters import (  # noqa: F401
     update_sp_aurora_params,
     use_ring_attn,
 )
+from .rope import apply_rope, rope_copy, rope_tables  # noqa: F401
 from .mpi_utils import (  # noqa: F401
     cleanup_distributed,
     detect_mpi_environment,

@@ -101,6 +101,9 @@ _SIGNATURES = {
     "spa_permute_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64),
                                    C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_int64,
                                    C.c_void_p]),
+    "spa_rope_rows": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_int64), C.POINTER(C.c_int64),
+                                C.POINTER(C.c_int64), C.c_int32, C.c_int32, C.c_void_p, C.c_void_p,
+                                C.c_int64, C.c_int32, C.c_int64, C.c_int32, C.c_void_p]),
     "spa_device_info": (C.c_int, [C.c_int32, C.POINTER(C.c_int64)]),
     "spa_check_status": (C.c_int, []),
     "spa_launch_count": (C.c_int64, []),

@@ -165,7 +165,7 @@ def all_to_all_5D(input: torch.Tensor, scatter_idx: int = 3, gather_idx: int = 1
     return out
 
 
-def heads_all_to_all_packed(tensors, group=None, copy_fn: Callable = strided_copy):
+def heads_all_to_all_packed(tensors, group=None, copy_fn: Callable = strided_copy, rope=None):
     """Sequence -> head reshard of several [B, S/P, H_i, D] tensors (q, k, v with their
     own head counts) as ONE all-to-all message instead of one per tensor
     (sp_aurora/intel_ulysses_attn.py:156-170 sends q, k and v separately).
@@ -173,10 +173,19 @@ def heads_all_to_all_packed(tensors, group=None, copy_fn: Callable = strided_cop
     The message is laid out (P, B, S/P, sum_i H_i/P, D): every token row carries its q
     heads, then its k heads, then its v heads. Returns [B, S, H_i/P, D] views of the
     gathered buffer (last dimension contiguous, row stride sum_i H_i/P * D), which the
-    attention kernels read in place."""
+    attention kernels read in place.
+
+    `rope` = (cos, sin, pos_offset, n_rotated): the first n_rotated tensors (q and k) are
+    rotated by the rotary embedding while they are packed (one pass instead of two);
+    pos_offset is the global position of this rank's first token."""
     P = _world(group)
     if P == 1:
-        return list(tensors)
+        if rope is None:
+            return list(tensors)
+        from .rope import rope_copy
+        cos, sin, pos_off, n_rot = rope
+        return [rope_copy(torch.empty_like(t), t, cos, sin, 1, pos_off) if i < n_rot else t
+                for i, t in enumerate(tensors)]
     B, Sl, _, D = tensors[0].shape
     hs = []
     for t in tensors:
@@ -188,8 +197,13 @@ def heads_all_to_all_packed(tensors, group=None, copy_fn: Callable = strided_cop
     hsum = sum(hs)
     send = torch.empty((P, B, Sl, hsum, D), dtype=tensors[0].dtype, device=tensors[0].device)
     o = 0
-    for t, h in zip(tensors, hs):
-        copy_fn(send[:, :, :, o:o + h], t.unflatten(2, (P, h)).permute(2, 0, 1, 3, 4))
+    for i, (t, h) in enumerate(zip(tensors, hs)):
+        dst, src = send[:, :, :, o:o + h], t.unflatten(2, (P, h)).permute(2, 0, 1, 3, 4)
+        if rope is not None and i < rope[3]:
+            from .rope import rope_copy
+            rope_copy(dst, src, rope[0], rope[1], 2, rope[2])    # dims (P, B, S_local, h): position = dim 2
+        else:
+            copy_fn(dst, src)
         o += h
     recv = _exchange(send, group)                           # [P_src, B, Sl, hsum, D]
     if B == 1:

@@ -545,6 +545,126 @@ bool force_simt() {
 }
 
 }  // namespace
+// ---------------------------------------------------------------------------
+// Rotary position embedding fused into a strided row copy (the Ulysses pack of q and k, or a
+// plain in-layout rotation): dst[..., :D/2] = x1*cos - x2*sin, dst[..., D/2:] = x2*cos + x1*sin
+// with x1, x2 the two halves of a head row ("rotate-half" convention) and cos/sin fp32 tables
+// [table_rows, D/2] indexed by the token position = pos_offset + index along logical dim
+// pos_dim. `inverse` negates sin (the gradient of the rotation). A thread moves one 16-byte
+// vector of each half; HBM-bound: 2*N*elt bytes plus the (L2-resident) tables.
+struct RopeParams {
+  int64_t n[4];
+  int64_t ss[4];   // element strides
+  int64_t ds[4];
+  int64_t total;   // vector pairs
+  int64_t pos_off;
+  int pos_dim, D;
+  float sin_sign;
+};
+
+template <typename T>
+struct RopeVec {
+  static constexpr int kElts = 16 / sizeof(T);
+  __device__ static void unpack(const uint4& v, float* f);
+  __device__ static uint4 pack(const float* f);
+};
+template <>
+__device__ void RopeVec<float>::unpack(const uint4& v, float* f) {
+  f[0] = __uint_as_float(v.x); f[1] = __uint_as_float(v.y);
+  f[2] = __uint_as_float(v.z); f[3] = __uint_as_float(v.w);
+}
+template <>
+__device__ uint4 RopeVec<float>::pack(const float* f) {
+  return make_uint4(__float_as_uint(f[0]), __float_as_uint(f[1]), __float_as_uint(f[2]), __float_as_uint(f[3]));
+}
+template <>
+__device__ void RopeVec<__nv_bfloat16>::unpack(const uint4& v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ uint4 RopeVec<__nv_bfloat16>::pack(const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+template <>
+__device__ void RopeVec<__half>::unpack(const uint4& v, float* f) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 x = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+    f[2 * i] = x.x;
+    f[2 * i + 1] = x.y;
+  }
+}
+template <>
+__device__ uint4 RopeVec<__half>::pack(const float* f) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __half2 h = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&h);
+  }
+  return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kStreamBlock)
+rope_rows_kernel(const T* __restrict__ src, T* __restrict__ dst, const float* __restrict__ cos_t,
+                 const float* __restrict__ sin_t, const RopeParams p) {
+  constexpr int E = RopeVec<T>::kElts;
+  const int half = p.D / 2;
+  const int64_t ppr = half / E;                       // vector pairs per row
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < p.total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int c = (int)(i % ppr) * E;
+    int64_t r = i / ppr;
+    int64_t idx[4];
+    idx[3] = r % p.n[3]; r /= p.n[3];
+    idx[2] = r % p.n[2]; r /= p.n[2];
+    idx[1] = r % p.n[1]; r /= p.n[1];
+    idx[0] = r;
+    int64_t so = c, dof = c;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      so += idx[k] * p.ss[k];
+      dof += idx[k] * p.ds[k];
+    }
+    const int64_t pos = p.pos_off + idx[p.pos_dim];
+    const uint4 lo = __ldcs(reinterpret_cast<const uint4*>(src + so));
+    const uint4 hi = __ldcs(reinterpret_cast<const uint4*>(src + so + half));
+    float x1[E], x2[E], cs[E], sn[E], y1[E], y2[E];
+    RopeVec<T>::unpack(lo, x1);
+    RopeVec<T>::unpack(hi, x2);
+    const float4* c4 = reinterpret_cast<const float4*>(cos_t + pos * half + c);
+    const float4* s4 = reinterpret_cast<const float4*>(sin_t + pos * half + c);
+#pragma unroll
+    for (int k = 0; k < E / 4; ++k) {
+      const float4 cv = __ldg(c4 + k), sv = __ldg(s4 + k);
+      cs[4 * k] = cv.x; cs[4 * k + 1] = cv.y; cs[4 * k + 2] = cv.z; cs[4 * k + 3] = cv.w;
+      sn[4 * k] = sv.x; sn[4 * k + 1] = sv.y; sn[4 * k + 2] = sv.z; sn[4 * k + 3] = sv.w;
+    }
+#pragma unroll
+    for (int k = 0; k < E; ++k) {
+      const float sk = sn[k] * p.sin_sign;
+      y1[k] = x1[k] * cs[k] - x2[k] * sk;
+      y2[k] = x2[k] * cs[k] + x1[k] * sk;
+    }
+    __stcs(reinterpret_cast<uint4*>(dst + dof), RopeVec<T>::pack(y1));
+    __stcs(reinterpret_cast<uint4*>(dst + dof + half), RopeVec<T>::pack(y2));
+  }
+}
+
+
 }  // namespace spa
 
 using namespace spa;
@@ -868,6 +988,58 @@ int spa_permute_rows(const void* src, void* dst, const int64_t n[4], const int64
     permute_rows_kernel<int64_t><<<(unsigned)grid, block, 0, (cudaStream_t)stream>>>(
         (const uint8_t*)src, (uint8_t*)dst, p);
   int rc = check_launch("permute_rows");
+  if (rc == SPA_OK) note_launch();
+  return rc;
+}
+
+
+int spa_rope_rows(const void* src, void* dst, const int64_t n[4], const int64_t src_stride[4],
+                             const int64_t dst_stride[4], int32_t D, int32_t dtype, const float* cos_table,
+                             const float* sin_table, int64_t table_rows, int32_t pos_dim,
+                             int64_t pos_offset, int32_t inverse, void* stream) {
+  if (!src || !dst || !n || !src_stride || !dst_stride || !cos_table || !sin_table ||
+      !valid_head_dim(D) || pos_dim < 0 || pos_dim > 3 || pos_offset < 0) {
+    set_error("spa_rope_rows: bad argument");
+    return SPA_EINVAL;
+  }
+  const int es = elt_size(dtype);
+  if (es == 0) {
+    set_error("spa_rope_rows: unknown dtype %d", dtype);
+    return SPA_EINVAL;
+  }
+  if (((uintptr_t)src & 15) || ((uintptr_t)dst & 15) || ((uintptr_t)cos_table & 15) ||
+      ((uintptr_t)sin_table & 15)) {
+    set_error("spa_rope_rows: base pointers must be 16-byte aligned");
+    return SPA_EINVAL;
+  }
+  RopeParams p;
+  int64_t rows = 1;
+  for (int i = 0; i < 4; ++i) {
+    if (n[i] <= 0 || ((src_stride[i] * es) & 15) || ((dst_stride[i] * es) & 15)) {
+      set_error("spa_rope_rows: extents must be positive and strides multiples of 16 bytes");
+      return SPA_EINVAL;
+    }
+    p.n[i] = n[i];
+    p.ss[i] = src_stride[i];
+    p.ds[i] = dst_stride[i];
+    rows *= n[i];
+  }
+  if (pos_offset + n[pos_dim] > table_rows) {
+    set_error("spa_rope_rows: positions %lld..%lld exceed the %lld rows of the cos/sin tables",
+              (long long)pos_offset, (long long)(pos_offset + n[pos_dim] - 1), (long long)table_rows);
+    return SPA_EINVAL;
+  }
+  p.D = D;
+  p.pos_dim = pos_dim;
+  p.pos_off = pos_offset;
+  p.sin_sign = inverse ? -1.f : 1.f;
+  p.total = rows * ((D / 2) / (16 / es));
+  int64_t grid = (p.total + kStreamBlock - 1) / kStreamBlock;
+  const int64_t cap = 148 * 8 * 8;
+  if (grid > cap) grid = cap;
+  SPA_DISPATCH_T(dtype, rope_rows_kernel<T><<<(unsigned)grid, kStreamBlock, 0, (cudaStream_t)stream>>>(
+                            (const T*)src, (T*)dst, cos_table, sin_table, p));
+  int rc = check_launch("rope_rows");
   if (rc == SPA_OK) note_launch();
   return rc;
 }

@@ -337,3 +337,60 @@ def test_multi_gpu_parity(results, tag, error_log):
         ok, errs, el = res[tag]
         error_log[f"dist {tag} rank{r}"] = {"errs": errs, "lse": el}
         assert ok, f"rank {r} {tag}: errs {errs} lse {el}"
+
+
+def _rope_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    from sp_aurora_b200 import high_priority_nccl_options
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev,
+                            pg_options=high_priority_nccl_options())
+    res = {}
+    try:
+        import sp_aurora_b200 as spa
+        from sp_aurora_b200.all_to_all import heads_all_to_all_packed
+        from oracle import attention_oracle as orc
+        errs = []
+        for B in (1, 2):
+            S, hq, hkv, D = 64 * world, 2 * world, world, 64
+            gens = [torch.Generator().manual_seed(1500 + i) for i in range(3)]
+            qg = torch.randn(B, S, hq, D, generator=gens[0]).bfloat16()
+            kg = torch.randn(B, S, hkv, D, generator=gens[1]).bfloat16()
+            vg = torch.randn(B, S, hkv, D, generator=gens[2]).bfloat16()
+            cos, sin = spa.rope_tables(S, D, device=dev)
+            Sl = S // world
+            sl = slice(rank * Sl, (rank + 1) * Sl)
+            qo, ko, vo = heads_all_to_all_packed([t[:, sl].to(dev) for t in (qg, kg, vg)], None,
+                                                 rope=(cos, sin, rank * Sl, 2))
+            hs = lambda h: slice(rank * (h // world), (rank + 1) * (h // world))
+            rq = orc.rope_ref(qg, cos.cpu(), sin.cpu(), 1, 0)[:, :, hs(hq)]
+            rk = orc.rope_ref(kg, cos.cpu(), sin.cpu(), 1, 0)[:, :, hs(hkv)]
+            errs += _errs([(qo, rq), (ko, rk)])
+            errs.append(0.0 if torch.equal(vo.cpu(), vg[:, :, hs(hkv)]) else 1.0)   # v: plain permutation
+        res["rope_pack"] = (max(errs) <= 2e-2, errs, 0.0)
+    except Exception:  # noqa: BLE001
+        import traceback
+        res["error"] = traceback.format_exc()
+    ret[rank] = res
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.gpu
+def test_rope_fused_into_the_ulysses_pack():
+    """q and k rotated while they are packed for the sequence -> head all-to-all (one message,
+    positions offset by the rank's first token); v is the plain permutation, bit-exact."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    world = 4 if n >= 4 else 2
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_rope_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    for r in range(world):
+        res = dict(ret[r])
+        assert "error" not in res, res.get("error")
+        ok, errs, _ = res["rope_pack"]
+        assert ok, (r, errs)

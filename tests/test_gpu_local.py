@@ -453,3 +453,34 @@ def test_llama3_packed_stream_one_rank(spa):
         assert (lse[:, sl].cpu().double() - rl[0]).abs().max() <= 1e-3
         for got, want in ((qc.grad[sl], rdq[0]), (kc.grad[sl], rdk[0]), (vc.grad[sl], rdv[0])):
             assert (got.cpu().double() - want).abs().max() <= grad_tol(torch.bfloat16, want)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_rope_copy_matches_the_formula(spa, dtype):
+    """spa_rope_rows: rotated copy into a strided destination (the head slice of a packed
+    message), a position offset, the inverse rotation, and the autograd form."""
+    B, S, H, D, off = 2, 96, 4, 128, 37
+    cos, sin = spa.rope_tables(off + S, D, device="cuda")
+    x = _rand((B, S, H, D), dtype, 51)
+    ref = orc.rope_ref(x, cos.cpu(), sin.cpu(), 1, off)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    # into head slice [2, 6) of a wider buffer, sequence-major like the all-to-all message
+    wide = torch.zeros(B, S, 10, D, dtype=dtype, device="cuda")
+    spa.rope_copy(wide[:, :, 2:6], x.cuda(), cos, sin, 1, off)
+    assert (wide[:, :, 2:6].cpu().double() - ref).abs().max() <= tol
+    assert wide[:, :, :2].abs().max() == 0 and wide[:, :, 6:].abs().max() == 0
+    # permuted source view: positions along dim 2 of a [H, B, S, D] view
+    y = torch.empty(H, B, S, D, dtype=dtype, device="cuda")
+    spa.rope_copy(y, x.cuda().permute(2, 0, 1, 3), cos, sin, 2, off)
+    assert (y.permute(1, 2, 0, 3).cpu().double() - ref).abs().max() <= tol
+    # the inverse rotation undoes it (up to the rounding of the intermediate)
+    back = spa.rope_copy(torch.empty_like(y), y, cos, sin, 2, off, inverse=True)
+    assert (back.permute(1, 2, 0, 3).cpu().double() - x.double()).abs().max() <= 2 * tol
+    # autograd: gradient = inverse rotation of the incoming gradient
+    xg = x.cuda().requires_grad_(True)
+    g = _rand((B, S, H, D), dtype, 52)
+    spa.apply_rope(xg, cos, sin, pos_offset=off).backward(g.cuda())
+    want = orc.rope_ref(g, cos.cpu(), sin.cpu(), 1, off, inverse=True)
+    assert (xg.grad.cpu().double() - want).abs().max() <= tol
+    with pytest.raises(spa.SpaError):            # positions beyond the tables are refused
+        spa.rope_copy(torch.empty_like(y), y, cos, sin, 2, off + 1)

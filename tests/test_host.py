@@ -375,6 +375,30 @@ def test_reference_export_names_exist():
     assert spa.HAS_SPARSE_SAGE_ATTENTION is False
 
 
+def test_rope_arguments_are_validated_before_any_launch():
+    """spa_rope_rows refuses bad head dims, misaligned strides and positions beyond the cos/sin
+    tables with SPA_EINVAL (checked without a GPU: validation comes first)."""
+    from sp_aurora_b200 import _lib
+    lib = _lib.lib
+    EINVAL = -1                        # SPA_EINVAL of include/spa.h
+    buf = 0x10000                      # never dereferenced: the call is refused first
+    n, st = _lib.i64x4([1, 2, 8, 4]), _lib.i64x4([0, 8 * 4 * 64, 4 * 64, 64])
+    ok_args = (buf, buf, n, st, st, 64, 1, buf, buf, 8, 2, 0, 0, None)
+
+    def call(**kw):
+        names = ("src", "dst", "n", "ss", "ds", "D", "dtype", "cos", "sin", "rows", "pos_dim", "off", "inv",
+                 "stream")
+        a = dict(zip(names, ok_args))
+        a.update(kw)
+        return lib.spa_rope_rows(*[a[k] for k in names])
+    assert call(D=48) == EINVAL
+    assert call(off=1) == EINVAL                      # 8 positions from 1 exceed 8 table rows
+    assert call(pos_dim=4) == EINVAL
+    assert call(src=buf + 2) == EINVAL
+    assert call(ds=_lib.i64x4([0, 8 * 4 * 64, 4 * 64, 3])) == EINVAL
+    assert call(cos=None) == EINVAL
+
+
 def test_misaligned_arguments_are_refused_before_any_launch():
     """Vector loads need 16-byte aligned bases and strides: the C ABI answers
     SPA_EINVAL instead of faulting (checked without a GPU: validation comes first)."""
