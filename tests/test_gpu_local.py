@@ -359,14 +359,16 @@ def test_bounded_wait_gives_up_and_reports(spa):
     _check_fwd(spa, 1, 256, 256, 2, 2, 128, torch.bfloat16, True)
 
 
-def test_attention_block_matches_a_torch_reference(spa):
+@pytest.mark.parametrize("rope_base", [None, 10000.0])
+def test_attention_block_matches_a_torch_reference(spa, rope_base):
     """QKV projection -> attention -> output projection (the reference's example model shape,
     examples/example_mpi_integration.py:38-86) on one GPU, GQA, against the same block computed
-    with the CPU oracle between fp32 copies of the same projections; gradients of x included."""
+    with the CPU oracle between fp32 copies of the same projections; gradients of x included.
+    With rope_base, q and k are rotated between the projection and the attention."""
     torch.manual_seed(0)
     B, S, d_model, hq, hkv = 1, 384, 512, 4, 2
     D = d_model // hq
-    blk = spa.SequenceParallelAttentionBlock(d_model, hq, hkv, mode="ring", device="cuda")
+    blk = spa.SequenceParallelAttentionBlock(d_model, hq, hkv, mode="ring", device="cuda", rope_base=rope_base)
     x = (torch.randn(B, S, d_model) * 0.5).bfloat16()
     dy = (torch.randn(B, S, d_model) * 0.5).bfloat16()
     xc = x.cuda().requires_grad_(True)
@@ -378,6 +380,9 @@ def test_attention_block_matches_a_torch_reference(spa):
     xr = x.double().requires_grad_(True)
     qkv = (xr @ wq.t()).view(B, S, hq + 2 * hkv, D)
     q, k, v = qkv[:, :, :hq], qkv[:, :, hq:hq + hkv], qkv[:, :, hq + hkv:]
+    if rope_base is not None:
+        cos, sin = spa.rope_tables(S, D, rope_base)
+        q, k = orc.rope_ref(q, cos, sin, 1, 0), orc.rope_ref(k, cos, sin, 1, 0)
     g = hq // hkv
     qt = q.permute(0, 2, 1, 3)
     kt = k.permute(0, 2, 1, 3).repeat_interleave(g, dim=1)
