@@ -474,3 +474,61 @@ def test_bench_reference_arm_prints_contract_line():
     assert d["cpu_baseline"]["kind"] in ("port", "reference") and d["cpu_baseline"]["cores"] >= 1
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
     assert d["e2e"]["value"] == d["value"]
+
+
+@pytest.mark.parametrize("W", [2, 3, 4, 5, 8])
+def test_exchange_halves_message_matching_simulated(W, monkeypatch):
+    """exchange_halves for every rank of rings up to 8, simulated in one process: the posted
+    sends and receives are matched per (sender, receiver) pair in posting order, as NCCL and gloo
+    do, and the data must land in the right half-chunks -- to the zigzag layout and back, and
+    from the layout after W-1 hops (shift = W-1: where a finished dK|dV block sits) straight to
+    the contiguous owners."""
+    import torch.distributed as tdist
+    from sp_aurora_b200 import zigzag
+
+    class Op:
+        def __init__(self, fn, tensor, peer, group=None):
+            self.send, self.tensor, self.peer = fn is tdist.isend, tensor, peer
+
+    class Req:
+        def wait(self):
+            pass
+
+    posted = {}
+    current = {"rank": 0}
+    monkeypatch.setattr(zigzag, "_group_info", lambda group: (current["rank"], W))
+    monkeypatch.setattr(zigzag, "_global", lambda group, r: r)
+    monkeypatch.setattr(tdist, "P2POp", Op)
+    monkeypatch.setattr(tdist, "batch_isend_irecv",
+                        lambda ops: posted.setdefault(current["rank"], []).extend(ops) or [Req()])
+
+    def run(to_zigzag, shift, src_of, dst_of):
+        posted.clear()
+        finishers = []
+        for r in range(W):
+            current["rank"] = r
+            finishers.append(zigzag.exchange_halves([(src_of[r], dst_of[r])], None, to_zigzag, shift=shift,
+                                                    defer=True))
+        for s in range(W):
+            for d in range(W):
+                sends = [o for o in posted.get(s, []) if o.send and o.peer == d]
+                recvs = [o for o in posted.get(d, []) if not o.send and o.peer == s]
+                assert len(sends) == len(recvs), (s, d)
+                for a, b in zip(sends, recvs):
+                    b.tensor.copy_(a.tensor)
+        for f in finishers:
+            f()
+
+    h = 3
+    val = lambda c: torch.full((1, h, 2), float(c))          # half-chunk c carries the value c
+    contiguous = {r: [val(2 * r), val(2 * r + 1)] for r in range(W)}
+    zz = {r: [torch.empty(1, h, 2), torch.empty(1, h, 2)] for r in range(W)}
+    run(True, 0, contiguous, zz)
+    for r in range(W):
+        assert float(zz[r][0][0, 0, 0]) == r and float(zz[r][1][0, 0, 0]) == 2 * W - 1 - r
+    for shift in (0, W - 1):
+        held = {r: [val((r - shift) % W), val(2 * W - 1 - (r - shift) % W)] for r in range(W)}
+        back = {r: [torch.empty(1, h, 2), torch.empty(1, h, 2)] for r in range(W)}
+        run(False, shift, held, back)
+        for r in range(W):
+            assert float(back[r][0][0, 0, 0]) == 2 * r and float(back[r][1][0, 0, 0]) == 2 * r + 1, (shift, r)
