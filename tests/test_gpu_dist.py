@@ -394,3 +394,45 @@ def test_rope_fused_into_the_ulysses_pack():
         assert "error" not in res, res.get("error")
         ok, errs, _ = res["rope_pack"]
         assert ok, (r, errs)
+
+
+def _mpi_launch_worker(rank, world, port, ret):
+    sys.path.insert(0, ROOT)
+    for v in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MASTER_ADDR"):
+        os.environ.pop(v, None)
+    # what `mpiexec -n <world>` (Open MPI) gives each process on one node
+    os.environ.update(OMPI_COMM_WORLD_RANK=str(rank), OMPI_COMM_WORLD_SIZE=str(world),
+                      OMPI_COMM_WORLD_LOCAL_RANK=str(rank), OMPI_COMM_WORLD_LOCAL_SIZE=str(world),
+                      MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    res = {}
+    try:
+        import sp_aurora_b200 as spa
+        info = spa.setup_mpi_distributed()
+        t = torch.full((4,), float(rank + 1), device=info["device"])
+        dist.all_reduce(t)
+        q = torch.randn(1, 256, 2, 64, device=info["device"]).bfloat16()
+        out = spa.ring_flash_attn_func(q, q, q, causal=True)            # the ring over the new group
+        spa.check_status()
+        res = {"info": (info["rank"], info["world_size"], info["local_rank"], info["launcher"], info["backend"],
+                        str(info["device"])), "sum": float(t[0].item()), "finite": bool(torch.isfinite(out).all())}
+        spa.cleanup_distributed()
+    except Exception:  # noqa: BLE001
+        import traceback
+        res["error"] = traceback.format_exc()
+    ret[rank] = res
+
+
+@pytest.mark.gpu
+def test_mpi_style_launch_initialises_nccl():
+    """setup_mpi_distributed (sp_aurora/mpi_utils.py:293 in the reference) from an Open MPI style
+    environment: NCCL group bound to the rank's device, usable by the ring."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs at least two GPUs")
+    mgr = mp.Manager()
+    ret = mgr.dict()
+    mp.spawn(_mpi_launch_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    for r in range(2):
+        res = dict(ret[r])
+        assert "error" not in res, res.get("error")
+        assert res["info"] == (r, 2, r, "mpiexec", "nccl", f"cuda:{r}")
+        assert res["sum"] == 3.0 and res["finite"]
