@@ -113,3 +113,37 @@ def test_unsupported_arguments_raise(hooked):
         hf._ring_attention(q, q, q, is_causal=False, **kw)
     with pytest.raises(ValueError):
         hf._ring_attention(torch.randn(2, 8, 2, 8), q, q, **kw)
+
+
+def test_tiny_llama_runs_through_the_hook(hooked, monkeypatch):
+    """A two-layer Llama (GQA) from transformers with `_attn_implementation="sp_aurora"`: one
+    sequence against the eager model, and two sequences packed into one stream (position ids
+    restarting) against the eager model run on each sequence alone. Checks the layout, scaling
+    and GQA plumbing of the table entry with a torch stand-in for the kernel call."""
+    from transformers import LlamaConfig, LlamaModel
+    hf, fa_utils, table, _ = hooked
+
+    def stand_in(q, k, v, cu_seqlens_q, cu_seqlens_k, **kw):
+        kw.update(heads_k_stride=2, local_k_slice=slice(0, q.shape[0]))
+        return _fake_varlen(q, k, v, cu_seqlens_q, cu_seqlens_k, **kw)
+    monkeypatch.setattr(hf, "llama3_flash_attn_varlen_func", stand_in)
+    cfg = LlamaConfig(vocab_size=100, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                      num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=64)
+    torch.manual_seed(0)
+    model = LlamaModel(cfg).eval()
+    ids = torch.randint(0, 100, (1, 20))
+    with torch.no_grad():
+        ref_one = model(input_ids=ids).last_hidden_state
+        ref_a = model(input_ids=ids[:, :7]).last_hidden_state
+        ref_b = model(input_ids=ids[:, 7:]).last_hidden_state
+    hf.substitute_hf_flash_attn(None, heads_k_stride=1)
+    model.config._attn_implementation = "sp_aurora"
+    with torch.no_grad():
+        hf.update_ring_flash_attn_params([0, 20], None)
+        out_one = model(input_ids=ids).last_hidden_state
+        hf.update_ring_flash_attn_params([0, 7, 20], None)
+        pos = torch.cat((torch.arange(7), torch.arange(13)))[None]
+        out_packed = model(input_ids=ids, position_ids=pos).last_hidden_state
+    assert (out_one - ref_one).abs().max() <= 1e-5
+    assert (out_packed[:, :7] - ref_a).abs().max() <= 1e-5
+    assert (out_packed[:, 7:] - ref_b).abs().max() <= 1e-5
